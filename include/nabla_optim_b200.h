@@ -1,0 +1,301 @@
+/* nabla_optim_b200.h - C ABI of libnabla_optim_b200.so
+ *
+ * A B200 (sm_100a) implementation of the optimizer-step path of nabla-train:
+ * SGD / momentum, Adam, AdamW, parameter groups, LR schedules, dynamic loss
+ * scaling, global grad-norm clipping, a mixed-precision AdamW step and ZeRO-1
+ * sharding over NCCL.  Every entry point replaces one Rust interface of the
+ * reference; the citation beside each declaration is the file:line inside the
+ * nabla project (v0.10.0) whose behaviour it reproduces.
+ *
+ * Conventions
+ *   - Plain C99: opaque handle, pointers, sizes, doubles.  No exceptions, no
+ *     abort() across the boundary.
+ *   - Every function returns an nbo_status.  nbo_last_error() gives the text
+ *     of the last failure on that handle (or of the last handle-less failure
+ *     of the calling thread when passed NULL).
+ *   - Parameter and gradient pointers are DEVICE pointers owned by the caller
+ *     (what nabla's Tensor::device_ptr() returns,
+ *     nabla-core/src/common/tensor/mod.rs:132-134); tensors are contiguous.
+ *     The handle owns optimizer state (m, v, velocity, fp32 masters), its
+ *     tables and its scratch, all on the device given to nbo_create.
+ *   - Work is enqueued on the stream given to nbo_create (0 = the legacy
+ *     default stream).  Functions that return a device-computed scalar
+ *     (a norm, a skip decision) synchronise that stream before returning;
+ *     all others are asynchronous.
+ *   - One host thread drives a handle at a time.
+ *   - There is no CPU fallback: without a CUDA device nbo_create fails.
+ */
+#ifndef NABLA_OPTIM_B200_H
+#define NABLA_OPTIM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NBO_API __attribute__((visibility("default")))
+
+typedef struct nbo_optimizer nbo_optimizer;
+
+typedef enum {
+    NBO_OK = 0,
+    NBO_ERR_INVALID = 1, /* bad argument: null/misaligned pointer, count mismatch ... */
+    NBO_ERR_CUDA = 2,    /* a CUDA runtime call failed                              */
+    NBO_ERR_NCCL = 3,    /* an NCCL call failed                                     */
+    NBO_ERR_TIMEOUT = 4, /* a bounded wait ran out                                  */
+    NBO_ERR_STATE = 5,   /* call order violated (e.g. step before set_tensors)      */
+    NBO_ERR_NOMEM = 6    /* device or host allocation failed                        */
+} nbo_status;
+
+/* OptimKind, same order as nabla-train/src/optim/core.rs:46-51. */
+typedef enum { NBO_ADAMW = 0, NBO_ADAM = 1, NBO_SGD = 2 } nbo_kind;
+
+/* Element type of the caller's params/grads. */
+typedef enum {
+    NBO_F32 = 0,       /* params, grads and state all fp32 (Optimizer<f32, Cuda>)     */
+    NBO_MIXED_BF16 = 1 /* bf16 params+grads, fp32 master/m/v held by the handle       */
+} nbo_precision;
+
+/* One parameter group = ParamGroupConfig (nabla-train/src/optim/groups.rs:40-51).
+ * A plain optimizer is a handle with a single group. */
+typedef struct {
+    int32_t kind;        /* nbo_kind */
+    double lr;
+    double beta1;        /* Adam/AdamW; defaults .9  (alg.rs:29-37)  */
+    double beta2;        /*             defaults .999                */
+    double eps;          /*             defaults 1e-8                */
+    double weight_decay; /* AdamW default 0.01; Sgd default 0; ignored by Adam */
+    double momentum;     /* Sgd only (alg.rs:324-329)                */
+} nbo_group_config;
+
+/* GradScalerState (nabla-train/src/optim/core.rs:326-332). */
+typedef struct {
+    double scale;
+    double growth_factor;
+    double backoff_factor;
+    uint64_t growth_interval;
+    uint64_t consecutive_ok;
+} nbo_scaler_state;
+
+/* LrSchedule (nabla-train/src/optim/core.rs:101-121). */
+typedef enum {
+    NBO_SCHED_COSINE = 0,
+    NBO_SCHED_LINEAR = 1,
+    NBO_SCHED_ONECYCLE = 2,
+    NBO_SCHED_STEP = 3
+} nbo_schedule_kind;
+
+typedef struct {
+    int32_t kind;          /* nbo_schedule_kind               */
+    uint64_t warmup_steps; /* cosine, linear                  */
+    uint64_t total_steps;  /* cosine, linear, onecycle        */
+    double min_lr;         /* cosine                          */
+    double max_lr;         /* onecycle                        */
+    double pct_start;      /* onecycle                        */
+    uint64_t step_size;    /* step                            */
+    double gamma;          /* step                            */
+} nbo_lr_schedule;
+
+/* Outcome of one mixed-precision / ZeRO-1 step. */
+typedef struct {
+    int32_t applied;      /* 1 = update applied, 0 = skipped (non-finite grads)       */
+    int32_t nonfinite;    /* 1 = a non-finite gradient was seen                        */
+    double grad_norm;     /* pre-clip global L2 norm of the unscaled grads (0 if none) */
+    double loss_scale;    /* scale to use for the NEXT backward pass                   */
+    uint64_t step_count;  /* optimizer step count after this call (group 0)            */
+} nbo_step_result;
+
+/* ---- library ------------------------------------------------------------ */
+
+/* ABI version of this header; bumps on any incompatible change. */
+NBO_API int32_t nbo_abi_version(void);
+
+/* Text of the last error on `h`; with h == NULL, the calling thread's last
+ * handle-less error.  Never NULL. */
+NBO_API const char *nbo_last_error(const nbo_optimizer *h);
+
+/* ---- lifecycle ---------------------------------------------------------- */
+
+/* Creates an optimizer bound to CUDA device `device` and to `stream`
+ * (a cudaStream_t; NULL = legacy default stream; nabla's own stream is
+ * cuda_compute_stream(), nabla-core/src/cuda_hip/cuda/core.rs:618-620).
+ * Replaces the constructors Sgd::new / Adam::new / AdamW::new /
+ * GroupOptimizer::from_named_params (alg.rs:20-40,181-201,319-331;
+ * groups.rs:168-226) together with nbo_add_group and nbo_set_tensors. */
+NBO_API int32_t nbo_create(int32_t device, void *stream, nbo_optimizer **out);
+NBO_API int32_t nbo_destroy(nbo_optimizer *h);
+
+/* Appends a parameter group; *group_id receives its index (0, 1, ...).
+ * Must precede nbo_set_tensors.  (groups.rs:40-51, 204-218) */
+NBO_API int32_t nbo_add_group(nbo_optimizer *h, const nbo_group_config *cfg, int32_t *group_id);
+
+/* Declares the parameter list: `n` tensors with `numel[i]` elements, tensor i
+ * belonging to group `group_ids[i]` (NULL = all in group 0).  Allocates and
+ * zeroes the state (m, v / velocity; plus fp32 masters for NBO_MIXED_BF16),
+ * as the constructors do from `param_shapes` (alg.rs:20-40).  Zero-element
+ * tensors are allowed. */
+NBO_API int32_t nbo_set_tensors(nbo_optimizer *h, uint64_t n, const uint64_t *numel,
+                                const int32_t *group_ids, int32_t precision);
+
+/* ---- Optimizer trait (nabla-train/src/optim/core.rs:9-44) ---------------- */
+
+/* Optimizer::step(params, grads) for fp32 handles.  `n` must equal the count
+ * given to nbo_set_tensors, else NBO_ERR_INVALID with the reference's
+ * "params count mismatch" wording (alg.rs:110-119).  Pointers may change from
+ * call to call; an unchanged set reuses the device-resident table.
+ * SGD: alg.rs:382-416.  Adam: alg.rs:254-291.  AdamW: alg.rs:109-150. */
+NBO_API int32_t nbo_step(nbo_optimizer *h, uint64_t n, void *const *params,
+                         const void *const *grads);
+
+/* Optimizer::reset: zero the state and the Adam step counts (alg.rs:152-162). */
+NBO_API int32_t nbo_reset(nbo_optimizer *h);
+
+/* Optimizer::set_lr.  One group: overwrite lr (alg.rs:164-166).  Several
+ * groups: group k gets base_lr[k] * lr / base_lr[0]; if base_lr[0] <= 0 every
+ * group gets `lr` (groups.rs:301-312). */
+NBO_API int32_t nbo_set_lr(nbo_optimizer *h, double lr);
+NBO_API int32_t nbo_get_lr(const nbo_optimizer *h, int32_t group_id, double *lr);
+
+/* zero_grad (nabla-ml/src/autograd/ops.rs:1668-1673): every gradient of the
+ * bound list becomes zeros (memset on the stream).  `elem_size` 4 or 2. */
+NBO_API int32_t nbo_zero_grad(nbo_optimizer *h, uint64_t n, void *const *grads);
+
+/* ---- OptimState (nabla-train/src/optim/core.rs:64-79) -------------------- */
+
+/* Step count of a group (AdamW::step_count, alg.rs:76-79). */
+NBO_API int32_t nbo_step_count(const nbo_optimizer *h, int32_t group_id, uint64_t *count);
+NBO_API int32_t nbo_set_step_count(nbo_optimizer *h, int32_t group_id, uint64_t count);
+NBO_API int32_t nbo_get_group(const nbo_optimizer *h, int32_t group_id, nbo_group_config *cfg);
+NBO_API int32_t nbo_set_group(nbo_optimizer *h, int32_t group_id, const nbo_group_config *cfg);
+
+/* State tensors.  `which`: 0 = m (Adam/AdamW), 1 = v (Adam/AdamW) or the
+ * velocity (SGD - the reference names it v{i} too, alg.rs:620-640),
+ * 2 = fp32 master (mixed precision only).  `dst`/`src` are HOST buffers of
+ * numel[tensor] floats.  Synchronous. */
+NBO_API int32_t nbo_state_export(nbo_optimizer *h, uint64_t tensor, int32_t which, float *dst);
+NBO_API int32_t nbo_state_import(nbo_optimizer *h, uint64_t tensor, int32_t which,
+                                 const float *src);
+
+/* ---- GradScaler / clip_grad_norm on fp32 gradients ----------------------- */
+
+/* GradScaler state (core.rs:334-349,390-413).  A fresh handle holds the
+ * defaults: 65536, x2 every 2000 clean steps, x0.5 on overflow. */
+NBO_API int32_t nbo_scaler_get(const nbo_optimizer *h, nbo_scaler_state *out);
+NBO_API int32_t nbo_scaler_set(nbo_optimizer *h, const nbo_scaler_state *in);
+
+/* GradScaler::unscale_and_update (core.rs:351-388) on fp32 device gradients:
+ * non-finite test on the still-scaled values; on a hit the scale backs off,
+ * the counter resets, every gradient becomes zero and *ok = 0; otherwise each
+ * element is multiplied by f32(1/scale), the counter advances (growing the
+ * scale at the interval) and *ok = 1.  Synchronises the stream. */
+NBO_API int32_t nbo_unscale_and_update(nbo_optimizer *h, uint64_t n, void *const *grads,
+                                       int32_t *ok);
+
+/* clip_grad_norm (nabla-train/src/trainer.rs:500-523) on fp32 device
+ * gradients: *norm = sqrt(sum g^2) accumulated in f64; if norm > max_norm and
+ * norm > 0 every element is multiplied by f32(max_norm / norm).  max_norm <= 0
+ * returns 0.0 and changes nothing.  Synchronises the stream. */
+NBO_API int32_t nbo_clip_grad_norm(nbo_optimizer *h, uint64_t n, void *const *grads,
+                                   double max_norm, double *norm);
+
+/* Trainer::has_non_finite (trainer.rs:387-400) plus the norm in one pass:
+ * *nonfinite = 1 if any element is inf/NaN; *norm = global L2 norm (undefined
+ * when non-finite).  Does not modify the gradients.  Synchronises. */
+NBO_API int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *grads,
+                              double *norm, int32_t *nonfinite);
+
+/* ---- mixed-precision AdamW step ----------------------------------------- */
+
+/* Seeds the fp32 masters from the caller's bf16 params (exact widening), or
+ * from fp32 host values via nbo_state_import(which = 2). */
+NBO_API int32_t nbo_init_master_from_params(nbo_optimizer *h, uint64_t n,
+                                            const void *const *params_bf16);
+
+/* One fused training-step tail for NBO_MIXED_BF16 handles, in the order of
+ * Trainer::train_epoch_with_max_steps (trainer.rs:230-283):
+ *   GradScaler::unscale_and_update (if use_scaler) -> non-finite skip ->
+ *   clip_grad_norm(max_norm) (if max_norm > 0) -> Adam/AdamW on the fp32
+ *   masters -> bf16 params = round-to-nearest-even of the masters.
+ * The gradients are read twice (norm/non-finite pass, update pass) and never
+ * written.  A skipped step changes nothing but the scaler.  Synchronises the
+ * stream to fill `result`. */
+NBO_API int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
+                               const void *const *grads_bf16, int32_t use_scaler,
+                               double max_norm, nbo_step_result *result);
+
+/* ---- LR schedules (pure host math) --------------------------------------- */
+
+/* lr_at_step (nabla-train/src/optim/core.rs:130-173); `step` is the trainer's
+ * step before its increment. */
+NBO_API int32_t nbo_lr_at_step(const nbo_lr_schedule *schedule, double base_lr, uint64_t step,
+                               double *lr);
+
+/* ---- ZeRO-1 over NCCL (replaces nabla-train/src/dist.rs:7-44) ------------ */
+
+/* 128-byte NCCL unique id; rank 0 creates it and ships it to the other ranks
+ * by any host channel. */
+NBO_API int32_t nbo_zero1_unique_id(uint8_t id_out[128]);
+
+/* Shard geometry for `total` elements over `world` ranks: every rank owns
+ * *shard_elems elements, a multiple of 8 (so bf16 shards are 16-byte aligned);
+ * *padded_total = world * *shard_elems >= total.  Pure host arithmetic. */
+NBO_API int32_t nbo_zero1_geometry(uint64_t total, int32_t world, uint64_t *shard_elems,
+                                   uint64_t *padded_total);
+
+/* Declares the parameter list as one flat bf16 bucket in list order (tensor i
+ * starts where tensor i-1 ends; the bucket is padded_total elements long) and
+ * joins the NCCL communicator.  The handle then holds state only for the
+ * intersection of every tensor with this rank's shard
+ * [rank*shard, (rank+1)*shard).  Replaces nbo_set_tensors.  world == 1 makes
+ * no NCCL call at all. */
+NBO_API int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *numel,
+                               const int32_t *group_ids, int32_t rank, int32_t world,
+                               const uint8_t unique_id[128]);
+
+/* Seeds this rank's fp32 master shard from the flat bf16 param bucket. */
+NBO_API int32_t nbo_zero1_init_master(nbo_optimizer *h, const void *params_flat_bf16);
+
+/* One ZeRO-1 step on the flat buckets (both padded_total bf16 elements):
+ *   reduce-scatter(grads, sum or mean) -> shard norm^2 + non-finite flag ->
+ *   all-gather of the per-rank scalars, combined in rank order -> scaler /
+ *   skip / clip decision (identical on every rank) -> fused local update of
+ *   the shard -> all-gather(params).
+ * `average` != 0 divides the reduced gradients by `world` (ncclAvg). */
+NBO_API int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat_bf16, void *grads_flat_bf16,
+                               int32_t average, int32_t use_scaler, double max_norm,
+                               nbo_step_result *result);
+
+/* This rank's shard range in bucket elements and the number of table entries
+ * (tensor pieces) it holds. */
+NBO_API int32_t nbo_zero1_shard(const nbo_optimizer *h, uint64_t *begin, uint64_t *end,
+                                uint64_t *pieces);
+
+/* Copies this rank's fp32 state shard to a HOST buffer of shard_elems floats;
+ * `which` as in nbo_state_export.  Synchronous. */
+NBO_API int32_t nbo_zero1_state_export(nbo_optimizer *h, int32_t which, float *dst);
+
+/* ---- introspection ------------------------------------------------------- */
+
+/* Device timing of the kernels inside nbo_step / nbo_step_mixed / nbo_zero1_step.
+ * With `on` != 0 the handle records CUDA events on its stream around the norm
+ * pass and around the update launches of every later step (two extra event
+ * records each; no synchronisation is added).  nbo_profile_last returns the
+ * elapsed milliseconds of the most recent step's norm pass (0 if it had none)
+ * and update launches; it synchronises the stream.  No counterpart in the
+ * reference, whose profiler wraps host timers around whole ops
+ * (nabla-train/src/profiler.rs:177-197). */
+NBO_API int32_t nbo_profile(nbo_optimizer *h, int32_t on);
+NBO_API int32_t nbo_profile_last(nbo_optimizer *h, float *norm_ms, float *update_ms);
+
+/* Number of kernels the handle has launched since creation (all entry
+ * points), and the number of chunks in its multi-tensor table. */
+NBO_API int32_t nbo_launch_count(const nbo_optimizer *h, uint64_t *launches);
+NBO_API int32_t nbo_table_info(const nbo_optimizer *h, uint64_t *tensors, uint64_t *chunks,
+                               uint64_t *uploads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NABLA_OPTIM_B200_H */

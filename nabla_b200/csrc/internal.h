@@ -1,0 +1,140 @@
+// Host-side internals shared by the translation units of libnabla_optim_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/nabla_optim_b200.h"
+#include "types.h"
+
+namespace nbo {
+
+struct Group {
+    nbo_group_config cfg;
+    double base_lr;        // lr at creation: set_lr rescales from it (groups.rs:301-312)
+    uint64_t step_count;   // Adam/AdamW step counter (alg.rs:120-121)
+    uint32_t chunk_begin;  // this group's range in the chunk list
+    uint32_t chunk_end;
+};
+
+// One table entry on the host: a whole tensor, or under ZeRO-1 the part of a
+// tensor that falls into this rank's shard.
+struct Piece {
+    uint64_t tensor;      // index in the caller's list
+    uint64_t offset;      // first element of the piece inside its tensor
+    uint64_t n;           // elements
+    uint64_t state_off;   // element offset into the flat state arrays
+    uint64_t bucket_off;  // element offset into the flat bucket (ZeRO-1 only)
+    int32_t group;
+};
+
+struct Zero1;  // defined in zero1.cu
+
+}  // namespace nbo
+
+struct nbo_optimizer {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string err;
+
+    std::vector<nbo::Group> groups;
+
+    bool configured = false;
+    int precision = NBO_F32;
+    uint64_t ntensors = 0;             // length of the caller's list
+    std::vector<uint64_t> numel;       // per caller tensor
+    std::vector<int32_t> group_of;     // per caller tensor
+    std::vector<int64_t> piece_of;     // per caller tensor: its piece (non-ZeRO: identity), -1 if none
+    std::vector<nbo::Piece> pieces;    // the table rows
+
+    // flat state (fp32), one allocation each
+    uint64_t state_elems = 0;
+    float *d_s0 = nullptr, *d_s1 = nullptr, *d_s2 = nullptr;
+
+    // device table
+    nbo::TensorDesc *h_descs = nullptr;  // pinned staging, pieces.size() rows
+    nbo::TensorDesc *d_descs = nullptr;
+    nbo::Chunk *d_chunks = nullptr;
+    uint32_t nchunks = 0;
+    cudaEvent_t upload_done = nullptr;
+    bool table_bound = false;
+    uint64_t uploads = 0;
+    std::vector<const void *> bound_p, bound_g;  // last bound caller pointers
+
+    // reduction scratch and decision record
+    int max_grid = 0;
+    int sm_count = 0;
+    double *d_partial_sum = nullptr;
+    int32_t *d_partial_bad = nullptr;
+    uint32_t *d_ticket = nullptr;
+    double *d_local = nullptr;       // {sumsq, nonfinite} of the last norm launch
+    nbo::StepCtrl *d_ctrl = nullptr;
+    nbo::StepCtrl *h_ctrl = nullptr;  // pinned
+
+    // optional device timing (nbo_profile): [0,1] bracket the norm pass, [2,3] the update launches
+    bool profile = false;
+    bool prof_norm_valid = false, prof_update_valid = false;
+    cudaEvent_t prof_ev[4] = {nullptr, nullptr, nullptr, nullptr};
+
+    nbo_scaler_state scaler{65536.0, 2.0, 0.5, 2000, 0};
+    uint64_t launches = 0;
+
+    nbo::Zero1 *zero1 = nullptr;
+};
+
+namespace nbo {
+
+int32_t fail(nbo_optimizer *h, int32_t code, const std::string &msg);
+int32_t fail_cuda(nbo_optimizer *h, cudaError_t e, const char *what);
+
+#define NBO_CUDA(h, call)                                   \
+    do {                                                    \
+        cudaError_t e__ = (call);                           \
+        if (e__ != cudaSuccess)                             \
+            return nbo::fail_cuda((h), e__, #call);         \
+    } while (0)
+
+// f64::powi as the reference's toolchain computes it (square-and-multiply, low
+// bit first); used for the Adam bias corrections and the step LR schedule.
+double powi(double a, int32_t b);
+
+// Host scalars of one Adam/AdamW step narrowed to f32 once each (alg.rs:120-135).
+AdamHP adam_hparams(const nbo_group_config &c, uint64_t step, float inv_scale);
+SgdHP sgd_hparams(const nbo_group_config &c);
+
+// Frees and rebuilds table + state for the pieces already stored in h->pieces.
+int32_t build_table(nbo_optimizer *h);
+void free_table(nbo_optimizer *h);
+
+// Points the table rows at caller memory.  Either argument may be null (keep
+// what is bound).  Re-uploads only when a pointer changed.
+int32_t bind_list(nbo_optimizer *h, uint64_t n, void *const *params, const void *const *grads,
+                  int elem_size, const char *who);
+// ZeRO-1: rows point into the two flat buckets.
+int32_t bind_flat(nbo_optimizer *h, void *params_flat, const void *grads_flat);
+
+// Kernel launches (kernels.cu), all on h->stream.  Ranges are in chunk-list
+// entries; every launcher counts itself in h->launches.
+int32_t launch_adam_f32(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const AdamHP &hp);
+int32_t launch_sgd_f32(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const SgdHP &hp);
+int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const AdamHP &hp,
+                          bool with_ctrl);
+int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize);
+int32_t launch_finalize_ranks(nbo_optimizer *h, const double *gathered, int world, double max_norm);
+int32_t launch_scale_grads(nbo_optimizer *h, int mode, float factor);
+int32_t launch_zero_grads(nbo_optimizer *h, bool bf16);
+int32_t launch_init_master(nbo_optimizer *h);
+
+// One adam_mixed launch per non-empty group, hyper-parameters for step_count + 1.
+int32_t launch_mixed_update(nbo_optimizer *h, float inv_scale, bool with_ctrl);
+// After the decision record reached the host: advance scaler + step counters.
+void commit_step(nbo_optimizer *h, bool checked, bool use_scaler, nbo_step_result *res);
+
+// Records profiling event `i` on the stream when profiling is on.
+int32_t prof_mark(nbo_optimizer *h, int i);
+
+void zero1_destroy(nbo_optimizer *h);
+
+}  // namespace nbo

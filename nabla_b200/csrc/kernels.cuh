@@ -1,0 +1,567 @@
+// Device code of libnabla_optim_b200: the multi-tensor-apply (MTA) kernels.
+//
+// Everything here is HBM-bound streaming work for sm_100a: each element is read
+// once and written once per pass, with 128-bit (fp32) / 64-bit (bf16) coalesced
+// accesses, a persistent grid sized from the SM count, and no shared-memory
+// staging (there is no reuse to stage for).  Tensor cores are not involved.
+//
+// Arithmetic contract: every fp32 statement is ONE correctly-rounded IEEE
+// operation (__fmul_rn / __fadd_rn / __fdiv_rn / __fsqrt_rn) in the order the
+// nabla CPU backend applies them (nabla-train/src/optim/alg.rs:136-149 with
+// nabla-core/src/cpu/mod.rs:211-223: scale is x*s, axpy is y + (a*x) with the
+// product rounded first).  The intrinsics also stop the compiler from
+// contracting a multiply and an add into an FMA.  The only deviation is
+// powf(x, 0.5f) -> __fsqrt_rn(x): the host libm's powf is not correctly
+// rounded, sqrt is, so the two can differ by 1 ulp on a small fraction of
+// inputs.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "types.h"
+
+namespace nbo {
+
+// ---- helpers ----------------------------------------------------------------
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ uint2 ld_stream(const uint2 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint2 *p, uint2 v) { __stcs(p, v); }
+
+// bf16 -> f32 is a 16-bit shift (half 2.7.1 bf16::to_f32).
+__device__ __forceinline__ float bf16_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// f32 -> bf16, round-to-nearest-even on the upper half, NaNs quieted with their
+// upper payload kept (half 2.7.1 bf16::from_f32; used by Scalar::from_f64 for
+// bf16, nabla-core/src/common/scalar/mod.rs:338-340).
+__device__ __forceinline__ uint32_t f32_to_bf16(float f)
+{
+    uint32_t u = __float_as_uint(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u)
+        return (u >> 16) | 0x0040u;
+    uint32_t up = ((u & 0x00008000u) != 0u) && ((u & 0x00017fffu) != 0u);
+    return (u >> 16) + up;
+}
+
+__device__ __forceinline__ bool is_nonfinite(float f)
+{
+    return (__float_as_uint(f) & 0x7f800000u) == 0x7f800000u;
+}
+
+// One element of Adam (decoupled = 0) or AdamW (decoupled = 1);
+// alg.rs:138-148 / 283-290.
+__device__ __forceinline__ void adam_elem(float &p, float g, float &m, float &v, const AdamHP &h)
+{
+    float mm = __fmul_rn(m, h.b1);
+    mm = __fadd_rn(mm, __fmul_rn(h.one_minus_b1, g));
+    float vv = __fmul_rn(v, h.b2);
+    float gs = __fmul_rn(g, g);
+    vv = __fadd_rn(vv, __fmul_rn(h.one_minus_b2, gs));
+    float den = __fadd_rn(__fsqrt_rn(__fmul_rn(vv, h.inv_bc2)), h.eps);
+    float u = __fdiv_rn(__fmul_rn(mm, h.ss), den);
+    float pp = p;
+    if (h.decoupled)
+        pp = __fmul_rn(pp, h.decay);
+    pp = __fadd_rn(pp, __fmul_rn(-1.0f, u));
+    p = pp;
+    m = mm;
+    v = vv;
+}
+
+// One element of Sgd::step (alg.rs:399-413).
+__device__ __forceinline__ void sgd_elem(float &p, float g, float &vel, const SgdHP &h)
+{
+    float ge = g;
+    if (h.use_wd)
+        ge = __fadd_rn(g, __fmul_rn(p, h.wd));
+    if (h.use_mu) {
+        vel = __fadd_rn(__fmul_rn(vel, h.mu), ge);
+        ge = vel;
+    }
+    p = __fadd_rn(p, __fmul_rn(h.nlr, ge));
+}
+
+// Geometry of one chunk of one tensor.
+struct ChunkView {
+    uint64_t item0;   // first element of the aligned body this chunk covers
+    uint32_t nitems;  // 4-element items in this chunk
+    uint64_t s_lo0, s_lo1;  // scalar range A: [s_lo0, s_lo1)  (head, first chunk only)
+    uint64_t s_hi0, s_hi1;  // scalar range B: [s_hi0, s_hi1)  (tail, last chunk only)
+};
+
+__device__ __forceinline__ ChunkView chunk_view(const TensorDesc &d, uint32_t cidx)
+{
+    ChunkView c;
+    if (d.head == 0xffffffffu) {  // unaligned tensor: plain element loop over the chunk
+        uint64_t b = (uint64_t)cidx * kChunkElems;
+        uint64_t e = b + kChunkElems < d.n ? b + kChunkElems : d.n;
+        c.item0 = 0; c.nitems = 0;
+        c.s_lo0 = b; c.s_lo1 = e; c.s_hi0 = c.s_hi1 = 0;
+        return c;
+    }
+    uint64_t head = d.head < d.n ? d.head : d.n;
+    uint64_t body_items = (d.n - head) >> 2;
+    uint64_t i0 = (uint64_t)cidx * kChunkItems;
+    uint64_t i1 = i0 + kChunkItems < body_items ? i0 + kChunkItems : body_items;
+    if (i0 > body_items) i0 = body_items;
+    c.item0 = head + (i0 << 2);
+    c.nitems = (uint32_t)(i1 > i0 ? i1 - i0 : 0);
+    c.s_lo0 = 0; c.s_lo1 = cidx == 0 ? head : 0;
+    // the tensor owns ceil(n / kChunkElems) chunks whatever its alignment; the final one takes the tail
+    bool last = ((uint64_t)cidx + 1) * kChunkElems >= d.n;
+    c.s_hi0 = head + (body_items << 2);
+    c.s_hi1 = last ? d.n : c.s_hi0;
+    return c;
+}
+
+// ---- fp32 Adam / AdamW --------------------------------------------------------
+
+__global__ void __launch_bounds__(kBlock)
+adam_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                uint32_t nchunks, AdamHP hp)
+{
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        float *P = (float *)d.p;
+        const float *G = (const float *)d.g;
+        float4 *p4 = (float4 *)(P + cv.item0);
+        const float4 *g4 = (const float4 *)(G + cv.item0);
+        float4 *m4 = (float4 *)(d.s0 + cv.item0);
+        float4 *v4 = (float4 *)(d.s1 + cv.item0);
+
+        float4 p[kItemsPerThread], g[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                g[u] = ld_stream(g4 + i);
+                p[u] = ld_stream(p4 + i);
+                m[u] = ld_stream(m4 + i);
+                v[u] = ld_stream(v4 + i);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                adam_elem(p[u].x, g[u].x, m[u].x, v[u].x, hp);
+                adam_elem(p[u].y, g[u].y, m[u].y, v[u].y, hp);
+                adam_elem(p[u].z, g[u].z, m[u].z, v[u].z, hp);
+                adam_elem(p[u].w, g[u].w, m[u].w, v[u].w, hp);
+                st_stream(p4 + i, p[u]);
+                st_stream(m4 + i, m[u]);
+                st_stream(v4 + i, v[u]);
+            }
+        }
+        // head / tail / unaligned elements
+        for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock)
+            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
+        for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock)
+            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
+    }
+}
+
+// ---- fp32 SGD (plain, weight decay, momentum) --------------------------------
+
+template <bool kMomentum>
+__global__ void __launch_bounds__(kBlock)
+sgd_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+               uint32_t nchunks, SgdHP hp)
+{
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        float *P = (float *)d.p;
+        const float *G = (const float *)d.g;
+        float4 *p4 = (float4 *)(P + cv.item0);
+        const float4 *g4 = (const float4 *)(G + cv.item0);
+        float4 *s4 = (float4 *)(d.s0 + cv.item0);
+
+        float4 p[kItemsPerThread], g[kItemsPerThread], s[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                g[u] = ld_stream(g4 + i);
+                p[u] = ld_stream(p4 + i);
+                if (kMomentum) s[u] = ld_stream(s4 + i);
+                else s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                sgd_elem(p[u].x, g[u].x, s[u].x, hp);
+                sgd_elem(p[u].y, g[u].y, s[u].y, hp);
+                sgd_elem(p[u].z, g[u].z, s[u].z, hp);
+                sgd_elem(p[u].w, g[u].w, s[u].w, hp);
+                st_stream(p4 + i, p[u]);
+                if (kMomentum) st_stream(s4 + i, s[u]);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                float vel = kMomentum ? d.s0[i] : 0.f;
+                sgd_elem(P[i], G[i], vel, hp);
+                if (kMomentum) d.s0[i] = vel;
+            }
+        }
+    }
+}
+
+// ---- mixed-precision Adam / AdamW ---------------------------------------------
+// Per element: g = bf16->f32 (exact); g *= inv_scale (GradScaler unscale,
+// core.rs:373-375); g *= clip_scale (clip_grad_norm, trainer.rs:516-520);
+// Adam/AdamW on the fp32 master; bf16 param = RNE(master).  Reads 14 B, writes
+// 14 B per element.  Returns at once when the norm pass flagged the step as
+// skipped.
+
+__device__ __forceinline__ void mixed_elem(float g, float &w, float &m, float &v, const AdamHP &hp,
+                                           float clip)
+{
+    g = __fmul_rn(g, hp.inv_scale);
+    g = __fmul_rn(g, clip);
+    adam_elem(w, g, m, v, hp);
+}
+
+__global__ void __launch_bounds__(kBlock)
+adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                  uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl)
+{
+    float clip = 1.0f;
+    if (ctrl != nullptr) {
+        if (ctrl->skip)
+            return;
+        clip = ctrl->clip_scale;
+    }
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        uint16_t *P = (uint16_t *)d.p;
+        const uint16_t *G = (const uint16_t *)d.g;
+        uint2 *p2 = (uint2 *)(P + cv.item0);
+        const uint2 *g2 = (const uint2 *)(G + cv.item0);
+        float4 *m4 = (float4 *)(d.s0 + cv.item0);
+        float4 *v4 = (float4 *)(d.s1 + cv.item0);
+        float4 *w4 = (float4 *)(d.s2 + cv.item0);
+
+        uint2 g[kItemsPerThread];
+        float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                g[u] = ld_stream(g2 + i);
+                w[u] = ld_stream(w4 + i);
+                m[u] = ld_stream(m4 + i);
+                v[u] = ld_stream(v4 + i);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                mixed_elem(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
+                uint2 o;
+                o.x = f32_to_bf16(w[u].x) | (f32_to_bf16(w[u].y) << 16);
+                o.y = f32_to_bf16(w[u].z) | (f32_to_bf16(w[u].w) << 16);
+                st_stream(w4 + i, w[u]);
+                st_stream(m4 + i, m[u]);
+                st_stream(v4 + i, v[u]);
+                st_stream(p2 + i, o);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                mixed_elem(bf16_to_f32(G[i]), d.s2[i], d.s0[i], d.s1[i], hp, clip);
+                P[i] = (uint16_t)f32_to_bf16(d.s2[i]);
+            }
+        }
+    }
+}
+
+// fp32 master <- exact widening of the bf16 params.
+__global__ void __launch_bounds__(kBlock)
+init_master_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                   uint32_t nchunks)
+{
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const uint16_t *P = (const uint16_t *)d.p;
+        uint64_t b = (uint64_t)ck.index * kChunkElems;
+        uint64_t e = b + kChunkElems < d.n ? b + kChunkElems : d.n;
+        for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
+            d.s2[i] = bf16_to_f32(P[i]);
+    }
+}
+
+// ---- global L2 norm + non-finite flag -------------------------------------------
+// Pass 1 (all CTAs): every thread accumulates (g*inv_scale)^2 in f64 - the
+// square of an f32 is exact in f64, so this is the reference's `sum += v*v`
+// (trainer.rs:505-513) up to summation order - and ORs a non-finite flag taken
+// on the still-scaled value (core.rs:356-366).  Warp shuffles, then one shared
+// memory step, give one partial per CTA.
+// Pass 2 (the last CTA to finish, found with a self-resetting atomicInc
+// ticket): adds the partials in index order with a fixed tree, so the result
+// does not depend on CTA scheduling, and writes the StepCtrl record.
+
+__device__ __forceinline__ double shfl_down_f64(double x, int off)
+{
+    int lo = __double2loint(x), hi = __double2hiint(x);
+    lo = __shfl_down_sync(0xffffffffu, lo, off);
+    hi = __shfl_down_sync(0xffffffffu, hi, off);
+    return __hiloint2double(hi, lo);
+}
+
+// Sum over the block in a fixed order; valid in thread 0.
+__device__ __forceinline__ double block_sum_f64(double x, int &flag)
+{
+    __shared__ double s_sum[kBlock / 32];
+    __shared__ int s_flag[kBlock / 32];
+    for (int off = 16; off > 0; off >>= 1) {
+        x += shfl_down_f64(x, off);
+        flag |= __shfl_down_sync(0xffffffffu, flag, off);
+    }
+    int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();  // protect s_* against a previous use
+    if (l == 0) { s_sum[w] = x; s_flag[w] = flag; }
+    __syncthreads();
+    if (w == 0) {
+        x = l < kBlock / 32 ? s_sum[l] : 0.0;
+        flag = l < kBlock / 32 ? s_flag[l] : 0;
+        for (int off = 4; off > 0; off >>= 1) {
+            x += shfl_down_f64(x, off);
+            flag |= __shfl_down_sync(0xffffffffu, flag, off);
+        }
+    }
+    return x;
+}
+
+__device__ __forceinline__ void sq_acc(float g, float inv_scale, double &acc, int &bad)
+{
+    bad |= is_nonfinite(g) ? 1 : 0;
+    double x = (double)__fmul_rn(g, inv_scale);
+    acc = fma(x, x, acc);  // x*x is exact in f64, so this equals mul-then-add
+}
+
+struct NormOut {
+    double *partial_sum;   // [gridDim.x]
+    int32_t *partial_bad;  // [gridDim.x]
+    uint32_t *ticket;      // zero before the first launch; wraps back to zero by itself
+    double *local;         // [2]: {sumsq, nonfinite} of this launch (for the cross-rank exchange)
+    StepCtrl *ctrl;        // written when finalize != 0
+};
+
+__device__ __forceinline__ void write_ctrl(StepCtrl *ctrl, double sum, int bad, double max_norm)
+{
+    double norm = sqrt(sum);
+    StepCtrl c;
+    c.sumsq = sum;
+    c.norm = norm;
+    c.do_clip = (max_norm > 0.0 && norm > max_norm && norm > 0.0) ? 1 : 0;
+    c.clip_scale = c.do_clip ? (float)(max_norm / norm) : 1.0f;
+    c.nonfinite = bad;
+    c.skip = bad;
+    *ctrl = c;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kBlock)
+norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+            uint32_t nchunks, float inv_scale, double max_norm, int finalize, NormOut out)
+{
+    double acc = 0.0;
+    int bad = 0;
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        if (kBf16) {
+            const uint16_t *G = (const uint16_t *)d.g;
+            const uint2 *g2 = (const uint2 *)(G + cv.item0);
+            uint2 g[kItemsPerThread];
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < cv.nitems) g[u] = ld_stream(g2 + i);
+            }
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < cv.nitems) {
+                    sq_acc(bf16_to_f32(g[u].x & 0xffffu), inv_scale, acc, bad);
+                    sq_acc(bf16_to_f32(g[u].x >> 16), inv_scale, acc, bad);
+                    sq_acc(bf16_to_f32(g[u].y & 0xffffu), inv_scale, acc, bad);
+                    sq_acc(bf16_to_f32(g[u].y >> 16), inv_scale, acc, bad);
+                }
+            }
+            for (int r = 0; r < 2; ++r) {
+                uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+                for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
+                    sq_acc(bf16_to_f32(G[i]), inv_scale, acc, bad);
+            }
+        } else {
+            const float *G = (const float *)d.g;
+            const float4 *g4 = (const float4 *)(G + cv.item0);
+            float4 g[kItemsPerThread];
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < cv.nitems) g[u] = ld_stream(g4 + i);
+            }
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < cv.nitems) {
+                    sq_acc(g[u].x, inv_scale, acc, bad);
+                    sq_acc(g[u].y, inv_scale, acc, bad);
+                    sq_acc(g[u].z, inv_scale, acc, bad);
+                    sq_acc(g[u].w, inv_scale, acc, bad);
+                }
+            }
+            for (int r = 0; r < 2; ++r) {
+                uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+                for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
+                    sq_acc(G[i], inv_scale, acc, bad);
+            }
+        }
+    }
+    double bsum = block_sum_f64(acc, bad);
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) {
+        out.partial_sum[blockIdx.x] = bsum;
+        out.partial_bad[blockIdx.x] = bad;
+        __threadfence();
+        uint32_t t = atomicInc(out.ticket, gridDim.x - 1);  // wraps to 0 after the last CTA
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    double tot = 0.0;
+    int anybad = 0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kBlock) {
+        tot += __ldcg(out.partial_sum + i);
+        anybad |= __ldcg(out.partial_bad + i);
+    }
+    tot = block_sum_f64(tot, anybad);
+    if (threadIdx.x == 0) {
+        out.local[0] = tot;
+        out.local[1] = anybad ? 1.0 : 0.0;
+        if (finalize)
+            write_ctrl(out.ctrl, tot, anybad, max_norm);
+    }
+}
+
+// Cross-rank finalize: `gathered` holds {sumsq, nonfinite} of every rank in
+// rank order; every rank adds them in that order and so reaches the same
+// decision bit for bit.
+__global__ void finalize_ranks_kernel(const double *__restrict__ gathered, int world,
+                                      double max_norm, StepCtrl *ctrl)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0)
+        return;
+    double tot = 0.0;
+    int bad = 0;
+    for (int r = 0; r < world; ++r) {
+        tot += gathered[2 * r];
+        bad |= gathered[2 * r + 1] != 0.0 ? 1 : 0;
+    }
+    write_ctrl(ctrl, tot, bad, max_norm);
+}
+
+// ---- in-place fp32 gradient rewrite ---------------------------------------------
+// mode 0: GradScaler::unscale_and_update tail - zero everything when the norm
+//         pass saw a non-finite value, else g *= factor (core.rs:367-376).
+// mode 1: clip_grad_norm tail - g *= ctrl->clip_scale when ctrl->do_clip, else
+//         nothing is touched (trainer.rs:515-521).
+__global__ void __launch_bounds__(kBlock)
+scale_grads_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                   uint32_t nchunks, int mode, float factor, const StepCtrl *__restrict__ ctrl)
+{
+    bool zero = false;
+    if (mode == 0) {
+        zero = ctrl->nonfinite != 0;
+    } else {
+        if (!ctrl->do_clip)
+            return;
+        factor = ctrl->clip_scale;
+    }
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        float *G = (float *)d.g;
+        float4 *g4 = (float4 *)(G + cv.item0);
+        float4 g[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems && !zero) g[u] = ld_stream(g4 + i);
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                float4 o;
+                if (zero) {
+                    o = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else {
+                    o.x = __fmul_rn(g[u].x, factor);
+                    o.y = __fmul_rn(g[u].y, factor);
+                    o.z = __fmul_rn(g[u].z, factor);
+                    o.w = __fmul_rn(g[u].w, factor);
+                }
+                st_stream(g4 + i, o);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
+                G[i] = zero ? 0.f : __fmul_rn(G[i], factor);
+        }
+    }
+}
+
+// zero_grad: every gradient element becomes +0 (nabla-ml/src/autograd/ops.rs:1668-1673).
+template <bool kBf16>
+__global__ void __launch_bounds__(kBlock)
+zero_grads_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                  uint32_t nchunks)
+{
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        if (kBf16) {
+            uint16_t *G = (uint16_t *)d.g;
+            uint2 *g2 = (uint2 *)(G + cv.item0);
+            for (uint32_t i = threadIdx.x; i < cv.nitems; i += kBlock)
+                st_stream(g2 + i, make_uint2(0u, 0u));
+            for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock) G[i] = 0;
+            for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock) G[i] = 0;
+        } else {
+            float *G = (float *)d.g;
+            float4 *g4 = (float4 *)(G + cv.item0);
+            for (uint32_t i = threadIdx.x; i < cv.nitems; i += kBlock)
+                st_stream(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+            for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock) G[i] = 0.f;
+            for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock) G[i] = 0.f;
+        }
+    }
+}
+
+}  // namespace nbo

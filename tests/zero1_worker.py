@@ -1,0 +1,80 @@
+"""One rank of the multi-GPU ZeRO-1 check (launched by tests/test_gpu_zero1.py under torch.distributed.run).
+
+Every rank holds its own bf16 gradients.  After N sharded steps each rank checks that
+  (1) the parameter bucket is identical on all ranks, and
+  (2) a world = 1 optimizer on the same GPU, fed the reduced gradients the sharded step actually used
+      (gathered from the in-place reduce-scatter output), produces bit-identical parameters - i.e.
+      sharding changes where an element is updated, never its value.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import nabla_b200 as nb  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    sizes = [5, 4096, 3, 70001, 1, 8192, 2, 100000]
+    total = sum(sizes)
+    uid = nb.exchange_unique_id(rank, world)
+    z = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], rank, world, uid)
+    ref = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], 0, 1)      # single-GPU twin, full bucket
+    padded = z.padded
+    assert ref.padded <= padded
+    g0 = torch.Generator(device="cuda").manual_seed(1234)
+    pflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+    pflat[:total] = (torch.randn(total, device="cuda", generator=g0) * 0.02).to(torch.bfloat16)
+    pref = pflat[:ref.padded].clone()
+    z.init_master(pflat)
+    ref.init_master(pref)
+    gr = torch.Generator(device="cuda").manual_seed(99 + rank)
+    for step in range(3):
+        for use_scaler, max_norm in ((False, 0.0),):
+            gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+            gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4).to(torch.bfloat16)
+            res = z.step(pflat, gflat, average=True, use_scaler=use_scaler, max_norm=max_norm)
+            assert res.applied
+            # the reduced gradients each rank used sit in its slice of gflat
+            b, e, _ = z.shard_range()
+            parts = [torch.empty(z.shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+            dist.all_gather(parts, gflat[b:e].contiguous())
+            gfull = torch.cat(parts)[:ref.padded].contiguous()
+            r2 = ref.step(pref, gfull, use_scaler=use_scaler, max_norm=max_norm)
+            assert r2.applied
+            assert torch.equal(pflat[:total].view(torch.int16), pref[:total].view(torch.int16)), \
+                f"rank {rank} step {step}: sharded params differ from the single-GPU twin"
+    # clipping + scaler on: the decision is taken from all-gathered per-rank sums, identical everywhere
+    gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+    gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4 * 65536).to(torch.bfloat16)
+    if rank == world - 1:
+        gflat[7] = float("inf")              # lands in rank 0's shard after the reduce-scatter
+    before = pflat.clone()
+    res = z.step(pflat, gflat, average=False, use_scaler=True, max_norm=1.0)
+    assert not res.applied and res.nonfinite and res.loss_scale == 32768.0, (rank, res)
+    assert torch.equal(before.view(torch.int16), pflat.view(torch.int16))
+    gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4 * 32768).to(torch.bfloat16)
+    res = z.step(pflat, gflat, average=True, use_scaler=True, max_norm=1e-3)
+    assert res.applied and res.grad_norm > 1e-3
+    norms = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
+    dist.all_gather(norms, torch.tensor([res.grad_norm], dtype=torch.float64, device="cuda"))
+    assert all(float(n) == res.grad_norm for n in norms), "grad norm differs between ranks"
+    # identical parameters on every rank
+    digest = pflat.view(torch.int16).to(torch.int64).sum().reshape(1)
+    digests = [torch.zeros_like(digest) for _ in range(world)]
+    dist.all_gather(digests, digest)
+    assert all(int(d) == int(digest) for d in digests)
+    dist.barrier()
+    if rank == 0:
+        print("ZERO1_WORKER_OK", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
