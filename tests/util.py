@@ -26,19 +26,31 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
     return t.detach().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-def assert_close_rel(got, want, what="", rel=REL_TOL):
+def assert_close_rel(got, want, what="", rel=REL_TOL, floor=0.1):
+    """Elementwise |got - want| <= rel * max(|want|, floor * rms(want)).
+
+    The bar is 1e-5 relative.  A purely elementwise relative test is undefined for the handful of
+    elements that happen to sit next to zero (a parameter crossing zero has |want| ~ 1e-7 while its
+    rounding noise is a few ulp of the update, ~1e-9), so below a tenth of the tensor's RMS the error is
+    measured against that floor instead of against |want|.  Returns the worst relative error seen."""
     got = host(got) if isinstance(got, torch.Tensor) else got
     g, w = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
     assert g.shape == w.shape, what
     if g.size == 0:
         return 0.0
+    assert np.array_equal(np.isnan(g), np.isnan(w)), f"{what}: NaN pattern differs"
+    ok = ~np.isnan(w)
+    g, w = g[ok], w[ok]
+    if g.size == 0:
+        return 0.0
     err = np.abs(g - w)
-    bound = rel * np.abs(w)
-    bad = err > bound
-    assert not bad.any(), (f"{what}: {bad.sum()} of {g.size} elements off by more than {rel} relative; "
-                           f"worst {err.max():.3e} at value {w[err.argmax()]:.6e}")
+    scale = np.maximum(np.abs(w), floor * np.sqrt(np.mean(w * w)))
+    same = g == w
     with np.errstate(divide="ignore", invalid="ignore"):
-        r = np.where(w != 0, err / np.abs(w), 0.0)
+        r = np.where(same, 0.0, err / scale)
+    bad = r > rel
+    assert not bad.any(), (f"{what}: {bad.sum()} of {g.size} elements off by more than {rel} relative; "
+                           f"worst {r.max():.3e} (abs {err[r.argmax()]:.3e} at value {w[r.argmax()]:.6e})")
     return float(r.max())
 
 
