@@ -206,6 +206,30 @@ NBO_API int32_t nbo_clip_grad_norm(nbo_optimizer *h, uint64_t n, void *const *gr
 NBO_API int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *grads,
                               double *norm, int32_t *nonfinite);
 
+/* The norm / non-finite pass for callers that must not allocate: code running
+ * inside a stream capture, under an allocator that owns all device memory
+ * (nabla's pool allocator forbids raw cudaMalloc beside it), or with a fixed
+ * memory budget.  It has no counterpart in the reference.  It needs no handle
+ * and calls no cudaMalloc / cudaFree or any allocating routine: all scratch
+ * (table, chunk list, per-CTA partials, ticket) lives in one fixed
+ * ~280 KiB array in the library's device image, which every GPU that loads
+ * the library holds until exit.
+ *   grads     one contiguous DEVICE buffer of n elements, fp32 (NBO_F32) or
+ *             bf16 (NBO_MIXED_BF16); n <= 134,217,728 (2^27), else
+ *             NBO_ERR_INVALID - larger buffers need a handle and nbo_grad_norm
+ *   inv_scale each element is multiplied by it (rounded to f32) before it is
+ *             squared; the non-finite test is on the unmultiplied value
+ *   out_dev   caller-owned DEVICE buffer of two doubles, written on `stream`:
+ *             out_dev[0] = sum of squares (the norm is its sqrt),
+ *             out_dev[1] = 1.0 if any element is inf/NaN else 0.0
+ * Asynchronous on `stream`.  The first call on a device looks up the device
+ * address of the scratch array (cudaGetSymbolAddress) and should therefore be
+ * made before any stream capture begins.  Every call shares the one scratch
+ * array: calls that may overlap on the GPU (different streams without an
+ * ordering between them) race on it and must be serialised by the caller. */
+NBO_API int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const void *grads, uint64_t n,
+                                      int32_t precision, float inv_scale, double *out_dev);
+
 /* ---- mixed-precision AdamW step ----------------------------------------- */
 
 /* Seeds the fp32 masters from the caller's bf16 params (exact widening), or

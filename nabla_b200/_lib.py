@@ -78,6 +78,8 @@ SIGNATURES = {
     "nbo_unscale_and_update": (C.c_int32, [_H, C.c_uint64, _PP, _I32P]),
     "nbo_clip_grad_norm": (C.c_int32, [_H, C.c_uint64, _PP, C.c_double, _F64P]),
     "nbo_grad_norm": (C.c_int32, [_H, C.c_uint64, _PP, _F64P, _I32P]),
+    "nbo_grad_norm_noalloc": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_float,
+                                          C.c_void_p]),
     "nbo_init_master_from_params": (C.c_int32, [_H, C.c_uint64, _PP]),
     "nbo_step_mixed": (C.c_int32, [_H, C.c_uint64, _PP, _PP, C.c_int32, C.c_double, C.POINTER(StepResult)]),
     "nbo_lr_at_step": (C.c_int32, [C.POINTER(LrScheduleC), C.c_double, C.c_uint64, _F64P]),

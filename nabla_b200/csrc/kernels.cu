@@ -117,3 +117,118 @@ int32_t launch_init_master(nbo_optimizer *h)
 }
 
 }  // namespace nbo
+
+// ---- gradient norm for callers that cannot allocate --------------------------------------
+//
+// Some callers of this library run where cudaMalloc is off limits: inside a
+// region that is being captured into a CUDA graph, under a framework allocator
+// that owns all device memory and forbids raw allocations (nabla's own pool,
+// nabla-core/src/cuda_hip/common/pool.rs, is one), or in a process that hands
+// this library a fixed memory budget.  A handle (nbo_create / nbo_set_tensors)
+// allocates its table, state and reduction scratch, so those callers cannot
+// use it.  nbo_grad_norm_noalloc gives them the norm / non-finite pass over one
+// contiguous gradient buffer with every byte of scratch in the fixed array
+// below, which each GPU that loads the library holds until the process exits.
+//
+// The scratch carries a one-row tensor table, the chunk list (8 bytes per
+// 4096 elements, which is what bounds the supported size), the per-CTA
+// partials, the ticket and the decision record.  All calls share it and it
+// keeps the previous call's contents: the set-up kernel rewrites the table and
+// zeroes the ticket on every call, and two calls that overlap on the GPU
+// (different streams, no dependency) race on it.
+
+namespace nbo {
+
+constexpr uint32_t kNoAllocMaxChunks = 32768;                                       // 256 KiB of chunk list
+constexpr uint64_t kNoAllocMaxElems = (uint64_t)kNoAllocMaxChunks * kChunkElems;    // 134,217,728 elements
+constexpr int kNoAllocMaxGrid = 2048;
+
+struct NoAllocScratch {
+    TensorDesc desc;
+    StepCtrl ctrl;
+    uint32_t ticket;
+    uint32_t pad;
+    double partial_sum[kNoAllocMaxGrid];
+    int32_t partial_bad[kNoAllocMaxGrid];
+    Chunk chunks[kNoAllocMaxChunks];
+};
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+// Device code may name the array directly; it fills the table for this call.
+__global__ void noalloc_setup_kernel(const void *grads, uint64_t n, uint32_t head, uint32_t nchunks)
+{
+    NoAllocScratch *s = reinterpret_cast<NoAllocScratch *>(g_noalloc_scratch);
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0) {
+        TensorDesc d;
+        d.p = nullptr; d.g = grads; d.s0 = d.s1 = d.s2 = nullptr;
+        d.n = n; d.head = head; d.group = 0;
+        s->desc = d;
+        s->ticket = 0;  // must start at zero whatever an earlier call left behind
+    }
+    if (i < nchunks) s->chunks[i] = Chunk{0u, i};
+}
+
+}  // namespace nbo
+
+extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const void *grads, uint64_t n,
+                                         int32_t precision, float inv_scale, double *out_dev)
+{
+    using namespace nbo;
+    static NoAllocScratch *scratch_of[64] = {nullptr};  // device address of the array, per device
+    static int sms_of[64] = {0};
+    if (device < 0 || device >= 64)
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_grad_norm_noalloc: device index out of range");
+    if (!out_dev || (n && !grads))
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_grad_norm_noalloc: null pointer");
+    if (precision != NBO_F32 && precision != NBO_MIXED_BF16)
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_grad_norm_noalloc: unknown precision");
+    if (n > kNoAllocMaxElems)
+        return fail(nullptr, NBO_ERR_INVALID,
+                    "nabla-optim-b200: nbo_grad_norm_noalloc: " + std::to_string(n) +
+                        " elements exceed the fixed scratch (max " + std::to_string(kNoAllocMaxElems) +
+                        "); use a handle and nbo_grad_norm instead");
+    const bool bf16 = precision == NBO_MIXED_BF16;
+    const uintptr_t es = bf16 ? 2 : 4;
+    if (((uintptr_t)grads & (es - 1)) || ((uintptr_t)out_dev & 7u))
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_grad_norm_noalloc: misaligned pointer");
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail_cuda(nullptr, e, "cudaSetDevice");
+    int32_t rc = [&]() -> int32_t {
+        if (!scratch_of[device]) {
+            // The array's name is only a host-side stand-in: ask the runtime for its address on THIS device.
+            void *p = nullptr;
+            NBO_CUDA(nullptr, cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            NBO_CUDA(nullptr, cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device));
+            scratch_of[device] = static_cast<NoAllocScratch *>(p);
+        }
+        NoAllocScratch *s = scratch_of[device];
+        cudaStream_t st = (cudaStream_t)stream;
+        uint32_t nchunks = (uint32_t)((n + kChunkElems - 1) / kChunkElems);
+        // elements before the first 16-byte (fp32) / 8-byte (bf16) boundary are handled one by one
+        uint32_t head = (uint32_t)((((bf16 ? 8u : 16u) - ((uintptr_t)grads & (bf16 ? 7u : 15u))) & (bf16 ? 7u : 15u)) / es);
+        uint32_t setup_blocks = nchunks / 256 + 1;
+        noalloc_setup_kernel<<<setup_blocks, 256, 0, st>>>(grads, n, head, nchunks);
+        NBO_CUDA(nullptr, cudaGetLastError());
+        int per_sm = 0;
+        const void *k = bf16 ? (const void *)norm_kernel<true> : (const void *)norm_kernel<false>;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kBlock, 0) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        long long grid = (long long)sms_of[device] * per_sm;
+        if (grid > kNoAllocMaxGrid) grid = kNoAllocMaxGrid;
+        if (grid > (long long)nchunks) grid = nchunks;
+        if (grid < 1) grid = 1;
+        NormOut out{s->partial_sum, s->partial_bad, &s->ticket, out_dev, &s->ctrl};
+        if (bf16)
+            norm_kernel<true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+        else
+            norm_kernel<false><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+        NBO_CUDA(nullptr, cudaGetLastError());
+        return NBO_OK;
+    }();
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    return rc;
+}
