@@ -207,7 +207,8 @@ NBO_API int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *g
                               double *norm, int32_t *nonfinite);
 
 /* The norm / non-finite pass for callers that must not allocate: code running
- * inside a stream capture, under an allocator that owns all device memory
+ * while a stream capture elsewhere in the process (global capture mode)
+ * makes cudaMalloc illegal, under an allocator that owns all device memory
  * (nabla's pool allocator forbids raw cudaMalloc beside it), or with a fixed
  * memory budget.  It has no counterpart in the reference.  It needs no handle
  * and calls no cudaMalloc / cudaFree or any allocating routine: all scratch

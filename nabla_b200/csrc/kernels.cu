@@ -120,8 +120,9 @@ int32_t launch_init_master(nbo_optimizer *h)
 
 // ---- gradient norm for callers that cannot allocate --------------------------------------
 //
-// Some callers of this library run where cudaMalloc is off limits: inside a
-// region that is being captured into a CUDA graph, under a framework allocator
+// Some callers of this library run where cudaMalloc is off limits: while some
+// thread of the process has a stream capture open in global mode (cudaMalloc is
+// then illegal process-wide), under a framework allocator
 // that owns all device memory and forbids raw allocations (nabla's own pool,
 // nabla-core/src/cuda_hip/common/pool.rs, is one), or in a process that hands
 // this library a fixed memory budget.  A handle (nbo_create / nbo_set_tensors)

@@ -1,5 +1,5 @@
 """GPU: nbo_grad_norm_noalloc - the gradient norm / non-finite pass for callers that may not allocate
-device memory (stream capture in progress, an allocator that owns the whole device, a fixed memory
+device memory (a stream capture open elsewhere in the process, an allocator that owns the whole device, a fixed memory
 budget).  It must agree with the handle-based nbo_grad_norm, which allocates its own scratch, on two
 calls in a row: the second call reuses the one fixed scratch array and sees whatever the first left there.
 
