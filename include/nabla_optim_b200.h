@@ -292,6 +292,30 @@ NBO_API int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat_bf16, void *g
                                int32_t average, int32_t use_scaler, double max_norm,
                                nbo_step_result *result);
 
+/* The same step with the two collectives fused into the kernels over NVLink /
+ * NVSwitch peer memory instead of issued as separate NCCL passes.  Both flat
+ * buckets must live in symmetric memory: every rank's bucket mapped into every
+ * process (`*_peers[r]` = this process's mapping of rank r's bucket, with
+ * `*_peers[rank] == *_local`), optionally with an NVSwitch multicast mapping
+ * (`*_mc`, may be NULL).  transport: 0 = choose (multicast when available and
+ * world >= 4, else peer), 1 = plain peer loads/stores, 2 = multimem
+ * ld_reduce / st through the switch.  World 2..16.  Replaces
+ * nabla-train/src/dist.rs:36-43 together with the update it feeds. */
+NBO_API int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local,
+                                           void *const *grads_peers, void *grads_mc,
+                                           void *params_local, void *const *params_peers,
+                                           void *params_mc, int32_t transport);
+
+/* One step on the attached buckets: stream-ordered barrier -> [reduce + norm
+ * pass when loss scaling or clipping is on, per-rank scalars all-gathered and
+ * combined in rank order] -> one kernel per group that reads the gradients of
+ * this rank's shard from every rank, updates the fp32 state and writes the
+ * bf16 params into every rank's bucket -> barrier.  The reduced gradients are
+ * left in this rank's slice of its own gradient bucket, as nbo_zero1_step
+ * leaves them.  Same result structure and skip semantics as nbo_zero1_step. */
+NBO_API int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scaler,
+                                     double max_norm, nbo_step_result *result);
+
 /* This rank's shard range in bucket elements and the number of table entries
  * (tensor pieces) it holds. */
 NBO_API int32_t nbo_zero1_shard(const nbo_optimizer *h, uint64_t *begin, uint64_t *end,

@@ -89,6 +89,9 @@ SIGNATURES = {
     "nbo_zero1_init_master": (C.c_int32, [_H, C.c_void_p]),
     "nbo_zero1_step": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_double,
                                    C.POINTER(StepResult)]),
+    "nbo_zero1_attach_symmetric": (C.c_int32, [_H, C.c_void_p, _PP, C.c_void_p, C.c_void_p, _PP, C.c_void_p,
+                                               C.c_int32]),
+    "nbo_zero1_step_fused": (C.c_int32, [_H, C.c_int32, C.c_int32, C.c_double, C.POINTER(StepResult)]),
     "nbo_zero1_shard": (C.c_int32, [_H, _U64P, _U64P, _U64P]),
     "nbo_zero1_state_export": (C.c_int32, [_H, C.c_int32, C.c_void_p]),
     "nbo_profile": (C.c_int32, [_H, C.c_int32]),

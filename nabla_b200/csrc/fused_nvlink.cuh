@@ -1,0 +1,248 @@
+// ZeRO-1 step fused with its collectives over NVLink / NVSwitch peer memory.
+//
+// Instead of reduce-scatter -> update -> all-gather as three passes with the
+// buckets crossing HBM between them, one kernel per rank reads the gradients of
+// its shard straight from every rank's bucket, updates its fp32 state, and
+// writes the bf16 result straight into every rank's parameter bucket.  The
+// buckets live in symmetric memory (every rank's allocation mapped into every
+// process; optionally an NVSwitch multicast mapping on top).  Two transports:
+//
+//   kPeer   plain 64-bit peer loads (one per rank, summed in fp32 in rank
+//           order, rounded once to bf16) and plain peer stores.  Per GPU and
+//           direction this moves 2 x (N-1)/N x bucket bytes.  Best for N = 2.
+//   kMcast  multimem.ld_reduce (the switch adds the N copies, fp32 accumulate)
+//           and multimem.st (the switch replicates the store).  Per GPU and
+//           direction: bucket x (1 + 1/N) bytes.  Best for N >= 4.
+//
+// Only plain loads/stores and multimem are used on remote memory: no TMA, no
+// cluster multicast.  The kernels contain no cross-GPU waits of their own; the
+// host orders them with stream-ordered NCCL barriers (see zero1.cu), so nothing
+// here can spin.
+//
+// The reduced gradient is also written back into this rank's own slice of its
+// gradient bucket (as an in-place reduce-scatter would leave it), which is what
+// the update then uses - so the value that was applied can be read back.
+#pragma once
+#include "kernels.cuh"
+
+namespace nbo {
+
+enum Transport { kLocal = 0, kPeer = 1, kMcast = 2 };
+
+__device__ __forceinline__ uint2 mc_ld_reduce_bf16x4(const void *mc_addr)
+{
+    uint2 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.bf16x2 {%0, %1}, [%2];"
+                 : "=r"(r.x), "=r"(r.y)
+                 : "l"(mc_addr)
+                 : "memory");
+    return r;
+}
+
+__device__ __forceinline__ void mc_st_b64(void *mc_addr, uint2 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};"
+                 :
+                 : "l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y))
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t scale_round_bf16(float sum, const PeerArgs &pa)
+{
+    if (pa.average) sum = __fmul_rn(sum, pa.inv_world);
+    return f32_to_bf16(sum);
+}
+
+// One item (4 bf16) of this rank's shard, reduced over all ranks.
+template <int kT>
+__device__ __forceinline__ uint2 reduce_item(const uint2 *g_local, const PeerArgs &pa)
+{
+    if (kT == kMcast) {
+        uint2 r = mc_ld_reduce_bf16x4((const char *)g_local + pa.g_mc);
+        if (pa.average) {
+            r.x = scale_round_bf16(bf16_to_f32(r.x & 0xffffu), pa) | (scale_round_bf16(bf16_to_f32(r.x >> 16), pa) << 16);
+            r.y = scale_round_bf16(bf16_to_f32(r.y & 0xffffu), pa) | (scale_round_bf16(bf16_to_f32(r.y >> 16), pa) << 16);
+        }
+        return r;
+    }
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    uint2 x[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (r < pa.world) x[r] = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (r < pa.world) {
+            a0 = __fadd_rn(a0, bf16_to_f32(x[r].x & 0xffffu));
+            a1 = __fadd_rn(a1, bf16_to_f32(x[r].x >> 16));
+            a2 = __fadd_rn(a2, bf16_to_f32(x[r].y & 0xffffu));
+            a3 = __fadd_rn(a3, bf16_to_f32(x[r].y >> 16));
+        }
+    uint2 o;
+    o.x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
+    o.y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
+    return o;
+}
+
+// One stray element (head / tail of a piece): always plain peer loads, rank order.
+__device__ __forceinline__ uint16_t reduce_elem(const uint16_t *g_local, const PeerArgs &pa)
+{
+    float a = 0.f;
+    for (int r = 0; r < pa.world; ++r)
+        a = __fadd_rn(a, bf16_to_f32(*(const volatile uint16_t *)((const char *)g_local + pa.g_peer[r])));
+    return (uint16_t)scale_round_bf16(a, pa);
+}
+
+template <int kT>
+__device__ __forceinline__ void publish_item(uint2 *p_local, uint2 v, const PeerArgs &pa)
+{
+    if (kT == kMcast) {
+        mc_st_b64((char *)p_local + pa.p_mc, v);
+    } else {
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < pa.world) __stcs((uint2 *)((char *)p_local + pa.p_peer[r]), v);
+    }
+}
+
+__device__ __forceinline__ void publish_elem(uint16_t *p_local, uint16_t v, const PeerArgs &pa)
+{
+    for (int r = 0; r < pa.world; ++r) *(uint16_t *)((char *)p_local + pa.p_peer[r]) = v;
+}
+
+// Fused reduce-scatter + Adam/AdamW + all-gather over this rank's shard.
+//   kIn  : where the gradient comes from - kLocal (already reduced into the
+//          local slice by an earlier pass), kPeer or kMcast (reduced here).
+//   kOut : how the bf16 params reach the other ranks - kPeer or kMcast.
+template <int kIn, int kOut>
+__global__ void __launch_bounds__(kBlock)
+zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                          uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl, PeerArgs pa)
+{
+    float clip = 1.0f;
+    if (ctrl != nullptr) {
+        if (ctrl->skip)
+            return;
+        clip = ctrl->clip_scale;
+    }
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        uint16_t *P = (uint16_t *)d.p;
+        uint16_t *G = (uint16_t *)d.g;
+        uint2 *p2 = (uint2 *)(P + cv.item0);
+        uint2 *g2 = (uint2 *)(G + cv.item0);
+        float4 *m4 = (float4 *)(d.s0 + cv.item0);
+        float4 *v4 = (float4 *)(d.s1 + cv.item0);
+        float4 *w4 = (float4 *)(d.s2 + cv.item0);
+
+        uint2 g[kItemsPerThread];
+        float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                w[u] = ld_stream(w4 + i);
+                m[u] = ld_stream(m4 + i);
+                v[u] = ld_stream(v4 + i);
+                if (kIn == kLocal || kIn == kMcast) g[u] = kIn == kLocal ? ld_stream(g2 + i) : reduce_item<kMcast>(g2 + i, pa);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                if (kIn == kPeer) g[u] = reduce_item<kPeer>(g2 + i, pa);
+                if (kIn != kLocal) st_stream(g2 + i, g[u]);
+                mixed_elem(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
+                mixed_elem(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
+                uint2 o;
+                o.x = f32_to_bf16(w[u].x) | (f32_to_bf16(w[u].y) << 16);
+                o.y = f32_to_bf16(w[u].z) | (f32_to_bf16(w[u].w) << 16);
+                st_stream(w4 + i, w[u]);
+                st_stream(m4 + i, m[u]);
+                st_stream(v4 + i, v[u]);
+                publish_item<kOut>(p2 + i, o, pa);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                uint16_t gi = kIn == kLocal ? G[i] : reduce_elem(G + i, pa);
+                if (kIn != kLocal) G[i] = gi;
+                mixed_elem(bf16_to_f32(gi), d.s2[i], d.s0[i], d.s1[i], hp, clip);
+                publish_elem(P + i, (uint16_t)f32_to_bf16(d.s2[i]), pa);
+            }
+        }
+    }
+}
+
+// Reduce-scatter fused with the norm / non-finite pass: the reduced gradient of
+// this rank's shard is written into the local slice and its sum of squares and
+// non-finite flag are produced in the same sweep (same two-stage reduction as
+// norm_kernel).  Used when clipping or loss scaling needs the global norm before
+// any element may be updated.
+template <int kIn>
+__global__ void __launch_bounds__(kBlock)
+zero1_reduce_norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                         uint32_t nchunks, float inv_scale, NormOut out, PeerArgs pa)
+{
+    double acc = 0.0;
+    int bad = 0;
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck.index);
+        uint16_t *G = (uint16_t *)d.g;
+        uint2 *g2 = (uint2 *)(G + cv.item0);
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                uint2 g = reduce_item<kIn>(g2 + i, pa);
+                st_stream(g2 + i, g);
+                sq_acc(bf16_to_f32(g.x & 0xffffu), inv_scale, acc, bad);
+                sq_acc(bf16_to_f32(g.x >> 16), inv_scale, acc, bad);
+                sq_acc(bf16_to_f32(g.y & 0xffffu), inv_scale, acc, bad);
+                sq_acc(bf16_to_f32(g.y >> 16), inv_scale, acc, bad);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                uint16_t gi = reduce_elem(G + i, pa);
+                G[i] = gi;
+                sq_acc(bf16_to_f32(gi), inv_scale, acc, bad);
+            }
+        }
+    }
+    double bsum = block_sum_f64(acc, bad);
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) {
+        out.partial_sum[blockIdx.x] = bsum;
+        out.partial_bad[blockIdx.x] = bad;
+        __threadfence();
+        uint32_t t = atomicInc(out.ticket, gridDim.x - 1);
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    double tot = 0.0;
+    int anybad = 0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kBlock) {
+        tot += __ldcg(out.partial_sum + i);
+        anybad |= __ldcg(out.partial_bad + i);
+    }
+    tot = block_sum_f64(tot, anybad);
+    if (threadIdx.x == 0) {
+        out.local[0] = tot;
+        out.local[1] = anybad ? 1.0 : 0.0;
+    }
+}
+
+}  // namespace nbo

@@ -127,6 +127,11 @@ int32_t launch_scale_grads(nbo_optimizer *h, int mode, float factor);
 int32_t launch_zero_grads(nbo_optimizer *h, bool bf16);
 int32_t launch_init_master(nbo_optimizer *h);
 
+// ZeRO-1 fused with its collectives over peer / multicast mappings (transport: 0 local, 1 peer, 2 multicast)
+int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const AdamHP &hp,
+                                  bool with_ctrl, const PeerArgs &pa, int in_transport, int out_transport);
+int32_t launch_zero1_reduce_norm(nbo_optimizer *h, float inv_scale, const PeerArgs &pa, int in_transport);
+
 // One adam_mixed launch per non-empty group, hyper-parameters for step_count + 1.
 int32_t launch_mixed_update(nbo_optimizer *h, float inv_scale, bool with_ctrl);
 // After the decision record reached the host: advance scaler + step counters.

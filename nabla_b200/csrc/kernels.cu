@@ -5,6 +5,7 @@
 
 #include "internal.h"
 #include "kernels.cuh"
+#include "fused_nvlink.cuh"
 
 namespace nbo {
 
@@ -113,6 +114,51 @@ int32_t launch_init_master(nbo_optimizer *h)
     if (h->nchunks == 0) return NBO_OK;
     int grid = grid_for(h, h->nchunks, (const void *)init_master_kernel);
     init_master_kernel<<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks);
+    return launched(h);
+}
+
+}  // namespace nbo
+
+// ---- ZeRO-1 fused with its collectives (fused_nvlink.cuh) ------------------------------------
+
+namespace nbo {
+
+template <int kIn, int kOut>
+static int32_t launch_fused_one(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
+                                const PeerArgs &pa)
+{
+    int grid = grid_for(h, nc, (const void *)zero1_fused_update_kernel<kIn, kOut>);
+    zero1_fused_update_kernel<kIn, kOut><<<grid, kBlock, 0, h->stream>>>(
+        h->d_descs, h->d_chunks + cb, nc, hp, with_ctrl ? h->d_ctrl : nullptr, pa);
+    return launched(h);
+}
+
+int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
+                                  const PeerArgs &pa, int in_transport, int out_transport)
+{
+    if (nc == 0) return NBO_OK;
+    if (out_transport == kMcast) {
+        if (in_transport == kLocal) return launch_fused_one<kLocal, kMcast>(h, cb, nc, hp, with_ctrl, pa);
+        if (in_transport == kMcast) return launch_fused_one<kMcast, kMcast>(h, cb, nc, hp, with_ctrl, pa);
+        return launch_fused_one<kPeer, kMcast>(h, cb, nc, hp, with_ctrl, pa);
+    }
+    if (in_transport == kLocal) return launch_fused_one<kLocal, kPeer>(h, cb, nc, hp, with_ctrl, pa);
+    if (in_transport == kMcast) return launch_fused_one<kMcast, kPeer>(h, cb, nc, hp, with_ctrl, pa);
+    return launch_fused_one<kPeer, kPeer>(h, cb, nc, hp, with_ctrl, pa);
+}
+
+int32_t launch_zero1_reduce_norm(nbo_optimizer *h, float inv_scale, const PeerArgs &pa, int in_transport)
+{
+    NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
+    if (in_transport == kMcast) {
+        int grid = grid_for(h, h->nchunks, (const void *)zero1_reduce_norm_kernel<kMcast>);
+        zero1_reduce_norm_kernel<kMcast><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
+                                                                        inv_scale, out, pa);
+    } else {
+        int grid = grid_for(h, h->nchunks, (const void *)zero1_reduce_norm_kernel<kPeer>);
+        zero1_reduce_norm_kernel<kPeer><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
+                                                                       inv_scale, out, pa);
+    }
     return launched(h);
 }
 

@@ -52,4 +52,17 @@ struct SgdHP {
     int32_t use_mu, use_wd;
 };
 
+// Where the other ranks' copies of the two flat buckets are mapped in this
+// process (symmetric memory), as byte offsets from this rank's own bucket so
+// that "address of element i on rank r" = local address + delta.
+constexpr int kMaxPeers = 16;
+struct PeerArgs {
+    int32_t world, rank;
+    int32_t average;      // divide the reduced gradient by world (mean) instead of summing
+    float inv_world;
+    int64_t g_mc, p_mc;   // delta to the NVSwitch multicast mapping of the bucket (0 = none)
+    int64_t g_peer[kMaxPeers];
+    int64_t p_peer[kMaxPeers];
+};
+
 }  // namespace nbo

@@ -25,6 +25,8 @@ struct NcclApi {
                                   cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t,
                               cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                              cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     std::string why;
 };
@@ -53,6 +55,7 @@ static NcclApi *nccl_api()
     NBO_SYM(CommAbort, "ncclCommAbort");
     NBO_SYM(ReduceScatter, "ncclReduceScatter");
     NBO_SYM(AllGather, "ncclAllGather");
+    NBO_SYM(AllReduce, "ncclAllReduce");
     NBO_SYM(GetErrorString, "ncclGetErrorString");
 #undef NBO_SYM
     return &api;
@@ -63,6 +66,12 @@ struct Zero1 {
     uint64_t total = 0, shard = 0, padded = 0, begin = 0, end = 0;
     ncclComm_t comm = nullptr;
     double *d_gathered = nullptr;  // {sumsq, nonfinite} of every rank, rank order
+    // fused path: symmetric-memory buckets
+    bool attached = false;
+    int transport = 0;             // 1 = plain peer loads/stores, 2 = NVSwitch multicast
+    void *g_local = nullptr, *p_local = nullptr;
+    PeerArgs pa{};
+    int32_t *d_barrier = nullptr;  // one int, all-reduced as a stream-ordered cross-rank barrier
 };
 
 static int32_t fail_nccl(nbo_optimizer *h, ncclResult_t r, const char *what)
@@ -85,6 +94,7 @@ void zero1_destroy(nbo_optimizer *h)
     Zero1 *z = h->zero1;
     if (z->comm) nccl_api()->CommDestroy(z->comm);
     cudaFree(z->d_gathered);
+    cudaFree(z->d_barrier);
     delete z;
     h->zero1 = nullptr;
 }
@@ -263,6 +273,101 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
         NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
                                     h->stream));
     }
+    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    commit_step(h, checked, use_scaler != 0, result);
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local, void *const *grads_peers,
+                                   void *grads_mc, void *params_local, void *const *params_peers,
+                                   void *params_mc, int32_t transport)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    Zero1 *z = h->zero1;
+    if (z->world < 2)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the fused path needs world >= 2; use nbo_zero1_step");
+    if (z->world > kMaxPeers)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: fused path supports at most 16 ranks");
+    if (!grads_local || !params_local || !grads_peers || !params_peers)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket or peer list");
+    if (transport == 0) transport = (grads_mc && params_mc && z->world >= 4) ? 2 : 1;
+    if (transport != 1 && transport != 2) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: unknown transport");
+    if (transport == 2 && (!grads_mc || !params_mc))
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: multicast transport needs both multicast mappings");
+    uintptr_t all = (uintptr_t)grads_local | (uintptr_t)params_local | (uintptr_t)grads_mc | (uintptr_t)params_mc;
+    for (int r = 0; r < z->world; ++r) {
+        if (!grads_peers[r] || !params_peers[r])
+            return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null peer mapping for rank " + std::to_string(r));
+        all |= (uintptr_t)grads_peers[r] | (uintptr_t)params_peers[r];
+    }
+    if (all & 15u) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: flat buckets must be 16-byte aligned");
+    if (grads_peers[z->rank] != grads_local || params_peers[z->rank] != params_local)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: peers[rank] must be this rank's own bucket");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    PeerArgs pa{};
+    pa.world = z->world; pa.rank = z->rank; pa.average = 0; pa.inv_world = 1.0f / (float)z->world;
+    pa.g_mc = grads_mc ? (int64_t)((intptr_t)grads_mc - (intptr_t)grads_local) : 0;
+    pa.p_mc = params_mc ? (int64_t)((intptr_t)params_mc - (intptr_t)params_local) : 0;
+    for (int r = 0; r < z->world; ++r) {
+        pa.g_peer[r] = (int64_t)((intptr_t)grads_peers[r] - (intptr_t)grads_local);
+        pa.p_peer[r] = (int64_t)((intptr_t)params_peers[r] - (intptr_t)params_local);
+    }
+    if (!z->d_barrier) {
+        NBO_CUDA(h, cudaMalloc(&z->d_barrier, sizeof(int32_t)));
+        NBO_CUDA(h, cudaMemset(z->d_barrier, 0, sizeof(int32_t)));
+    }
+    z->pa = pa; z->g_local = grads_local; z->p_local = params_local;
+    z->transport = transport; z->attached = true;
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scaler, double max_norm,
+                             nbo_step_result *result)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    Zero1 *z = h->zero1;
+    if (!z->attached)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_zero1_step_fused before nbo_zero1_attach_symmetric");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    NcclApi *a = nccl_api();
+    int32_t rc = bind_flat(h, z->p_local, z->g_local);
+    if (rc != NBO_OK) return rc;
+    PeerArgs pa = z->pa;
+    pa.average = average ? 1 : 0;
+
+    // every rank's gradients are final, and nobody still reads the old params, before any peer access
+    NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, h->stream));
+
+    bool checked = use_scaler || max_norm > 0.0;
+    float inv_scale = use_scaler ? (float)(1.0 / h->scaler.scale) : 1.0f;
+    h->prof_norm_valid = false;
+    int in_transport = z->transport;
+    if (checked) {
+        prof_mark(h, 0);
+        rc = launch_zero1_reduce_norm(h, inv_scale, pa, z->transport);
+        if (rc != NBO_OK) return rc;
+        prof_mark(h, 1);
+        NBO_NCCL(h, a->AllGather(h->d_local, z->d_gathered, 2, ncclDouble, z->comm, h->stream));
+        rc = launch_finalize_ranks(h, z->d_gathered, z->world, max_norm);
+        if (rc != NBO_OK) return rc;
+        in_transport = 0;  // the reduced gradient now sits in the local slice
+    }
+    prof_mark(h, 2);
+    for (Group &g : h->groups) {
+        uint32_t nc = g.chunk_end - g.chunk_begin;
+        if (nc == 0) continue;
+        AdamHP hp = adam_hparams(g.cfg, g.step_count + 1, inv_scale);
+        rc = launch_zero1_fused_update(h, g.chunk_begin, nc, hp, checked, pa, in_transport, z->transport);
+        if (rc != NBO_OK) return rc;
+    }
+    prof_mark(h, 3);
+    // every rank's parameter stores have landed everywhere before anyone uses the params
+    NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, h->stream));
+    if (checked)
+        NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
+                                    h->stream));
     NBO_CUDA(h, cudaStreamSynchronize(h->stream));
     commit_step(h, checked, use_scaler != 0, result);
     return NBO_OK;

@@ -114,6 +114,45 @@ class Zero1AdamW:
                                                  float(max_norm), C.byref(res)))
         return StepOutcome.from_c(res)
 
+    # ---- fused path over NVLink / NVSwitch peer memory -------------------------------------------
+    def attach_symmetric(self, group=None, transport: int = 0):
+        """Allocates the two flat bf16 buckets in symmetric memory (torch.distributed._symmetric_memory:
+        every rank's buffer mapped into every process, plus an NVSwitch multicast mapping when the fabric
+        offers one) and registers them for `step_fused`.  Returns (params_flat, grads_flat); the caller
+        fills them like ordinary tensors.  transport: 0 = choose, 1 = peer loads/stores, 2 = multicast."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        dev = torch.device("cuda", self._h.device)
+        bufs, handles = [], []
+        for _ in range(2):
+            t = symm.empty(self.padded, dtype=torch.bfloat16, device=dev)
+            hd = symm.rendezvous(t, group.group_name)
+            t.zero_()
+            bufs.append(t)
+            handles.append(hd)
+        (pflat, gflat), (ph, gh) = bufs, handles
+        if gh.buffer_ptrs[self.rank] != gflat.data_ptr() or ph.buffer_ptrs[self.rank] != pflat.data_ptr():
+            raise RuntimeError("symmetric memory: buffer_ptrs[rank] is not the local allocation")
+        gp = L.ptr_array(list(gh.buffer_ptrs))
+        pp = L.ptr_array(list(ph.buffer_ptrs))
+        gmc = C.c_void_p(gh.multicast_ptr) if gh.multicast_ptr else None
+        pmc = C.c_void_p(ph.multicast_ptr) if ph.multicast_ptr else None
+        self._h.check(self._h.lib.nbo_zero1_attach_symmetric(
+            self._h.h, C.c_void_p(gflat.data_ptr()), gp, gmc, C.c_void_p(pflat.data_ptr()), pp, pmc, transport))
+        self._symm = (pflat, gflat, ph, gh)          # keep the mappings alive
+        self.has_multicast = bool(gh.multicast_ptr and ph.multicast_ptr)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        return pflat, gflat
+
+    def step_fused(self, *, average: bool = False, use_scaler: bool = False, max_norm: float = 0.0) -> StepOutcome:
+        """One step on the attached buckets with reduce-scatter and all-gather fused into the kernels."""
+        res = L.StepResult()
+        self._h.check(self._h.lib.nbo_zero1_step_fused(self._h.h, 1 if average else 0, 1 if use_scaler else 0,
+                                                       float(max_norm), C.byref(res)))
+        return StepOutcome.from_c(res)
+
     def state_shard(self, which: int) -> torch.Tensor:
         """fp32 state of this rank's shard on the host: 0 = m, 1 = v, 2 = master."""
         out = torch.empty(self.shard, dtype=torch.float32)

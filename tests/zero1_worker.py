@@ -1,5 +1,11 @@
 """One rank of the multi-GPU ZeRO-1 check (launched by tests/test_gpu_zero1.py under torch.distributed.run).
 
+    zero1_worker.py [nccl|peer|mcast]
+
+nccl  : reduce-scatter / all-gather issued as NCCL collectives around the local update (nbo_zero1_step)
+peer  : collectives fused into the kernels with plain peer loads/stores (nbo_zero1_step_fused, transport 1)
+mcast : the same through NVSwitch multimem ld_reduce / st (transport 2)
+
 Every rank holds its own bf16 gradients.  After N sharded steps each rank checks that
   (1) the parameter bucket is identical on all ranks, and
   (2) a world = 1 optimizer on the same GPU, fed the reduced gradients the sharded step actually used
@@ -18,6 +24,7 @@ import nabla_b200 as nb  # noqa: E402
 
 
 def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "nccl"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
@@ -29,7 +36,24 @@ def main():
     padded = z.padded
     assert ref.padded <= padded
     g0 = torch.Generator(device="cuda").manual_seed(1234)
-    pflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+    if mode == "nccl":
+        pflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
+        gbuf = None
+    else:
+        pflat, gbuf = z.attach_symmetric(transport=1 if mode == "peer" else 2)
+        if mode == "mcast" and not z.has_multicast:
+            if rank == 0:
+                print("ZERO1_WORKER_SKIP no multicast mapping on this fabric")
+            dist.destroy_process_group()
+            return
+
+    def do_step(gflat, **kw):
+        if mode == "nccl":
+            return z.step(pflat, gflat, **kw), gflat
+        gbuf.copy_(gflat)
+        torch.cuda.synchronize()
+        return z.step_fused(**kw), gbuf
+
     pflat[:total] = (torch.randn(total, device="cuda", generator=g0) * 0.02).to(torch.bfloat16)
     pref = pflat[:ref.padded].clone()
     z.init_master(pflat)
@@ -39,7 +63,7 @@ def main():
         for use_scaler, max_norm in ((False, 0.0),):
             gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
             gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4).to(torch.bfloat16)
-            res = z.step(pflat, gflat, average=True, use_scaler=use_scaler, max_norm=max_norm)
+            res, gflat = do_step(gflat, average=(step != 1), use_scaler=use_scaler, max_norm=max_norm)
             assert res.applied
             # the reduced gradients each rank used sit in its slice of gflat
             b, e, _ = z.shard_range()
@@ -56,12 +80,26 @@ def main():
     if rank == world - 1:
         gflat[7] = float("inf")              # lands in rank 0's shard after the reduce-scatter
     before = pflat.clone()
-    res = z.step(pflat, gflat, average=False, use_scaler=True, max_norm=1.0)
+    res, gflat = do_step(gflat, average=False, use_scaler=True, max_norm=1.0)
     assert not res.applied and res.nonfinite and res.loss_scale == 32768.0, (rank, res)
     assert torch.equal(before.view(torch.int16), pflat.view(torch.int16))
+    gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
     gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4 * 32768).to(torch.bfloat16)
-    res = z.step(pflat, gflat, average=True, use_scaler=True, max_norm=1e-3)
+    res, gflat = do_step(gflat, average=True, use_scaler=True, max_norm=1e-3)
     assert res.applied and res.grad_norm > 1e-3
+    # the clipped, unscaled step against the single-GPU twin fed the same reduced gradients
+    b, e, _ = z.shard_range()
+    parts = [torch.empty(z.shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    dist.all_gather(parts, gflat[b:e].contiguous())
+    gfull = torch.cat(parts)[:ref.padded].contiguous()
+    st = ref._h.lib.nbo_scaler_set  # twin scaler: same scale as the sharded optimizer had for this step
+    import ctypes as C
+    sc = nb._lib.ScalerState(32768.0, 2.0, 0.5, 2000, 0)
+    ref._h.check(st(ref._h.h, C.byref(sc)))
+    r2 = ref.step(pref, gfull, use_scaler=True, max_norm=1e-3)
+    assert r2.applied and abs(r2.grad_norm - res.grad_norm) <= 1e-12 * res.grad_norm, (r2.grad_norm, res.grad_norm)
+    same = (pflat[:total].view(torch.int16) == pref[:total].view(torch.int16)).float().mean().item()
+    assert same > 0.9999, f"clipped step: only {same:.6f} of the params match the single-GPU twin"
     norms = [torch.zeros(1, dtype=torch.float64, device="cuda") for _ in range(world)]
     dist.all_gather(norms, torch.tensor([res.grad_norm], dtype=torch.float64, device="cuda"))
     assert all(float(n) == res.grad_norm for n in norms), "grad norm differs between ranks"
@@ -72,7 +110,7 @@ def main():
     assert all(int(d) == int(digest) for d in digests)
     dist.barrier()
     if rank == 0:
-        print("ZERO1_WORKER_OK", world)
+        print("ZERO1_WORKER_OK", world, mode)
     dist.destroy_process_group()
 
 
