@@ -30,6 +30,9 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout must carry the one JSON line only.
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per element, from the ncu captures summarised under profiles/
 # (small cases of the same kernels: 5.535 GB / 199,757,824 elements and 3.430 GB / 124,439,808 elements).
@@ -273,13 +276,23 @@ def run_ours(args, wl_name, wl):
         uid = nb.exchange_unique_id(rank, world)
         opt = nb.Zero1AdamW.adamw(wl["lr"], wl["wd"], shapes, rank, world, uid)
         padded, shard = opt.padded, opt.shard
-        pflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
-        gflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
+        fused = world > 1 and args.zero1_path != "nccl"
+        if fused:
+            # buckets in symmetric memory; the collectives are fused into the update kernels
+            tr = {"auto": 0, "peer": 1, "mcast": 2}[args.zero1_path]
+            pflat, gflat = opt.attach_symmetric(transport=tr)
+        else:
+            pflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
+            gflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
         fill_randn_bf16(pflat[:total], 0.02, torch.Generator(device=dev).manual_seed(7))
         fill_randn_bf16(gflat[:total], 1e-4, gen)
         opt.init_master(pflat)
         pp, gp = pflat.data_ptr(), gflat.data_ptr()
-        step = lambda: opt.step_ptrs(pp, gp, average=True, use_scaler=False, max_norm=0.0)
+        if fused:
+            step = lambda: opt.step_fused(average=True, use_scaler=False, max_norm=0.0)
+        else:
+            step = lambda: opt.step_ptrs(pp, gp, average=True, use_scaler=False, max_norm=0.0)
+        extra["zero1_path"] = ("fused-" + args.zero1_path) if fused else ("nccl" if world > 1 else "local")
         handle = opt._h
         b, e, _ = opt.shard_range()
         local_elems = max(0, min(e, total) - b)
@@ -292,7 +305,7 @@ def run_ours(args, wl_name, wl):
             for off in range(0, padded, ring_elems):
                 m = min(ring_elems, padded - off)
                 gflat[off:off + m].copy_(ring_in[:m], non_blocking=True)
-            opt.step_ptrs(pp, gp, average=True, use_scaler=False, max_norm=0.0)
+            step()
             ro = ring_out.numel()
             for off in range(b, e, ro):
                 m = min(ro, e - off)
@@ -415,6 +428,7 @@ def run_ours(args, wl_name, wl):
                    "samples": clocks["samples"]},
         "wall_ms_per_step": wall * 1e3 / args.steps,
     }
+    line["config"].update(extra)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         mixed = wl["kind"] != "f32"
         sample = min(calibrated_cpu_sample(12.0, mixed), total)
@@ -437,6 +451,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama8b_zero1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--zero1-path", choices=["auto", "peer", "mcast", "nccl"], default="auto",
+                    help="N > 1: collectives fused into the kernels (auto/peer/mcast) or issued through NCCL")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

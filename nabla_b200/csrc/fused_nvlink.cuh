@@ -84,6 +84,47 @@ __device__ __forceinline__ uint2 reduce_item(const uint2 *g_local, const PeerArg
     return o;
 }
 
+// Peer transport with the remote loads of the first kPrefetchRanks ranks issued
+// up front (together with the local state loads), so that enough bytes are in
+// flight to cover the NVLink round trip; ranks beyond that are fetched when the
+// item is reduced.
+constexpr int kPrefetchRanks = 4;
+
+struct PeerItem {
+    uint2 x[kPrefetchRanks];
+};
+
+__device__ __forceinline__ void peer_prefetch(PeerItem &it, const uint2 *g_local, const PeerArgs &pa)
+{
+#pragma unroll
+    for (int r = 0; r < kPrefetchRanks; ++r)
+        if (r < pa.world) it.x[r] = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+}
+
+__device__ __forceinline__ uint2 peer_reduce(const PeerItem &it, const uint2 *g_local, const PeerArgs &pa)
+{
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int r = 0; r < kPrefetchRanks; ++r)
+        if (r < pa.world) {
+            a0 = __fadd_rn(a0, bf16_to_f32(it.x[r].x & 0xffffu));
+            a1 = __fadd_rn(a1, bf16_to_f32(it.x[r].x >> 16));
+            a2 = __fadd_rn(a2, bf16_to_f32(it.x[r].y & 0xffffu));
+            a3 = __fadd_rn(a3, bf16_to_f32(it.x[r].y >> 16));
+        }
+    for (int r = kPrefetchRanks; r < pa.world; ++r) {
+        uint2 x = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+        a0 = __fadd_rn(a0, bf16_to_f32(x.x & 0xffffu));
+        a1 = __fadd_rn(a1, bf16_to_f32(x.x >> 16));
+        a2 = __fadd_rn(a2, bf16_to_f32(x.y & 0xffffu));
+        a3 = __fadd_rn(a3, bf16_to_f32(x.y >> 16));
+    }
+    uint2 o;
+    o.x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
+    o.y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
+    return o;
+}
+
 // One stray element (head / tail of a piece): always plain peer loads, rank order.
 __device__ __forceinline__ uint16_t reduce_elem(const uint16_t *g_local, const PeerArgs &pa)
 {
@@ -138,22 +179,25 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         float4 *w4 = (float4 *)(d.s2 + cv.item0);
 
         uint2 g[kItemsPerThread];
+        PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
+                if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
+                if (kIn == kMcast) g[u] = reduce_item<kMcast>(g2 + i, pa);
+                if (kIn == kLocal) g[u] = ld_stream(g2 + i);
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
                 v[u] = ld_stream(v4 + i);
-                if (kIn == kLocal || kIn == kMcast) g[u] = kIn == kLocal ? ld_stream(g2 + i) : reduce_item<kMcast>(g2 + i, pa);
             }
         }
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
-                if (kIn == kPeer) g[u] = reduce_item<kPeer>(g2 + i, pa);
+                if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
                 if (kIn != kLocal) st_stream(g2 + i, g[u]);
                 mixed_elem(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
                 mixed_elem(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
@@ -198,11 +242,21 @@ zero1_reduce_norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__re
         const ChunkView cv = chunk_view(d, ck.index);
         uint16_t *G = (uint16_t *)d.g;
         uint2 *g2 = (uint2 *)(G + cv.item0);
+        PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
+        uint2 gm[kItemsPerThread];
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
-                uint2 g = reduce_item<kIn>(g2 + i, pa);
+                if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
+                else gm[u] = reduce_item<kMcast>(g2 + i, pa);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                uint2 g = kIn == kPeer ? peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa) : gm[u];
                 st_stream(g2 + i, g);
                 sq_acc(bf16_to_f32(g.x & 0xffffu), inv_scale, acc, bad);
                 sq_acc(bf16_to_f32(g.x >> 16), inv_scale, acc, bad);
