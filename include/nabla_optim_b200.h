@@ -213,7 +213,7 @@ NBO_API int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *g
  * memory budget.  It has no counterpart in the reference.  It needs no handle
  * and calls no cudaMalloc / cudaFree or any allocating routine: all scratch
  * (table, chunk list, per-CTA partials, ticket) lives in one fixed
- * ~280 KiB array in the library's device image, which every GPU that loads
+ * ~536 KiB array in the library's device image, which every GPU that loads
  * the library holds until exit.
  *   grads     one contiguous DEVICE buffer of n elements, fp32 (NBO_F32) or
  *             bf16 (NBO_MIXED_BF16); n <= 134,217,728 (2^27), else

@@ -169,7 +169,7 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         uint16_t *P = (uint16_t *)d.p;
         uint16_t *G = (uint16_t *)d.g;
         uint2 *p2 = (uint2 *)(P + cv.item0);
@@ -239,7 +239,7 @@ zero1_reduce_norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__re
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         uint16_t *G = (uint16_t *)d.g;
         uint2 *g2 = (uint2 *)(G + cv.item0);
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];

@@ -66,17 +66,26 @@ int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const Adam
     return launched(h);
 }
 
+template <bool kBf16, bool kCheckEach>
+static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, int finalize, const NormOut &out)
+{
+    uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;  // one loop iteration takes kNormBatch chunks
+    int grid = grid_for(h, units, (const void *)norm_kernel<kBf16, kCheckEach>);
+    norm_kernel<kBf16, kCheckEach><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
+                                                                  inv_scale, max_norm, finalize, out);
+}
+
 int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize)
 {
     NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
+    // the flag can be read off the sum only while the unscale factor cannot overflow a finite gradient
+    bool each = !(inv_scale <= 1.0f);
     if (bf16) {
-        int grid = grid_for(h, h->nchunks, (const void *)norm_kernel<true>);
-        norm_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
-                                                          inv_scale, max_norm, finalize, out);
+        if (each) launch_norm_one<true, true>(h, inv_scale, max_norm, finalize, out);
+        else launch_norm_one<true, false>(h, inv_scale, max_norm, finalize, out);
     } else {
-        int grid = grid_for(h, h->nchunks, (const void *)norm_kernel<false>);
-        norm_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
-                                                           inv_scale, max_norm, finalize, out);
+        if (each) launch_norm_one<false, true>(h, inv_scale, max_norm, finalize, out);
+        else launch_norm_one<false, false>(h, inv_scale, max_norm, finalize, out);
     }
     return launched(h);
 }
@@ -177,7 +186,7 @@ int32_t launch_zero1_reduce_norm(nbo_optimizer *h, float inv_scale, const PeerAr
 // contiguous gradient buffer with every byte of scratch in the fixed array
 // below, which each GPU that loads the library holds until the process exits.
 //
-// The scratch carries a one-row tensor table, the chunk list (8 bytes per
+// The scratch carries a one-row tensor table, the chunk list (16 bytes per
 // 4096 elements, which is what bounds the supported size), the per-CTA
 // partials, the ticket and the decision record.  All calls share it and it
 // keeps the previous call's contents: the set-up kernel rewrites the table and
@@ -186,7 +195,7 @@ int32_t launch_zero1_reduce_norm(nbo_optimizer *h, float inv_scale, const PeerAr
 
 namespace nbo {
 
-constexpr uint32_t kNoAllocMaxChunks = 32768;                                       // 256 KiB of chunk list
+constexpr uint32_t kNoAllocMaxChunks = 32768;                                       // 512 KiB of chunk list
 constexpr uint64_t kNoAllocMaxElems = (uint64_t)kNoAllocMaxChunks * kChunkElems;    // 134,217,728 elements
 constexpr int kNoAllocMaxGrid = 2048;
 
@@ -214,7 +223,13 @@ __global__ void noalloc_setup_kernel(const void *grads, uint64_t n, uint32_t hea
         s->desc = d;
         s->ticket = 0;  // must start at zero whatever an earlier call left behind
     }
-    if (i < nchunks) s->chunks[i] = Chunk{0u, i};
+    if (i < nchunks) {
+        uint64_t h = head < n ? head : n;
+        uint64_t body_items = (n - h) >> 2, i0 = (uint64_t)i * kChunkItems;
+        uint64_t ni = i0 >= body_items ? 0 : (body_items - i0 < kChunkItems ? body_items - i0 : kChunkItems);
+        bool last = ((uint64_t)i + 1) * kChunkElems >= n;
+        s->chunks[i] = Chunk{0u, i, (uint32_t)ni, (i == 0 && h) || (last && ((n - h) & 3)) ? 1u : 0u};
+    }
 }
 
 }  // namespace nbo
@@ -261,18 +276,19 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
         noalloc_setup_kernel<<<setup_blocks, 256, 0, st>>>(grads, n, head, nchunks);
         NBO_CUDA(nullptr, cudaGetLastError());
         int per_sm = 0;
-        const void *k = bf16 ? (const void *)norm_kernel<true> : (const void *)norm_kernel<false>;
+        const void *k = bf16 ? (const void *)norm_kernel<true, true> : (const void *)norm_kernel<false, true>;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kBlock, 0) != cudaSuccess || per_sm < 1)
             per_sm = 1;
         long long grid = (long long)sms_of[device] * per_sm;
         if (grid > kNoAllocMaxGrid) grid = kNoAllocMaxGrid;
-        if (grid > (long long)nchunks) grid = nchunks;
+        long long units = ((long long)nchunks + kNormBatch - 1) / kNormBatch;
+        if (grid > units) grid = units;
         if (grid < 1) grid = 1;
         NormOut out{s->partial_sum, s->partial_bad, &s->ticket, out_dev, &s->ctrl};
         if (bf16)
-            norm_kernel<true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+            norm_kernel<true, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
         else
-            norm_kernel<false><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+            norm_kernel<false, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
         NBO_CUDA(nullptr, cudaGetLastError());
         return NBO_OK;
     }();

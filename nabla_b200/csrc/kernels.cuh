@@ -115,6 +115,21 @@ __device__ __forceinline__ ChunkView chunk_view(const TensorDesc &d, uint32_t ci
     return c;
 }
 
+// The same geometry from the chunk entry: the host has already counted the
+// items of every chunk, so the common case (aligned row, no stray elements)
+// costs one multiply-add instead of the 64-bit min/compare chain above.
+__device__ __forceinline__ ChunkView chunk_view(const TensorDesc &d, const Chunk &ck)
+{
+    if (!ck.stray && d.head != 0xffffffffu) {
+        ChunkView c;
+        c.item0 = d.head + (uint64_t)ck.index * kChunkElems;
+        c.nitems = ck.nitems;
+        c.s_lo0 = c.s_lo1 = c.s_hi0 = c.s_hi1 = 0;
+        return c;
+    }
+    return chunk_view(d, ck.index);
+}
+
 // ---- fp32 Adam / AdamW --------------------------------------------------------
 
 __global__ void __launch_bounds__(kBlock)
@@ -124,7 +139,7 @@ adam_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ 
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         float *P = (float *)d.p;
         const float *G = (const float *)d.g;
         float4 *p4 = (float4 *)(P + cv.item0);
@@ -174,7 +189,7 @@ sgd_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ c
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         float *P = (float *)d.p;
         const float *G = (const float *)d.g;
         float4 *p4 = (float4 *)(P + cv.item0);
@@ -243,7 +258,7 @@ adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict_
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         uint16_t *P = (uint16_t *)d.p;
         const uint16_t *G = (const uint16_t *)d.g;
         uint2 *p2 = (uint2 *)(P + cv.item0);
@@ -377,67 +392,112 @@ __device__ __forceinline__ void write_ctrl(StepCtrl *ctrl, double sum, int bad, 
     *ctrl = c;
 }
 
-template <bool kBf16>
+// Sum-of-squares accumulation without a per-element flag: any inf/NaN among the
+// inputs makes the f64 sum itself non-finite (squares cannot cancel, and finite
+// f32 squares cannot overflow f64), so the flag is read off the total.  That
+// equivalence needs |g * inv_scale| <= |g|, i.e. inv_scale <= 1; otherwise a
+// finite gradient could overflow in the f32 product and kCheckEach keeps the
+// explicit per-element test on the unmultiplied value.
+template <bool kCheckEach>
+__device__ __forceinline__ void sq_acc_fast(float g, float inv_scale, double &acc, int &bad)
+{
+    if (kCheckEach) bad |= is_nonfinite(g) ? 1 : 0;
+    double x = (double)__fmul_rn(g, inv_scale);
+    acc = fma(x, x, acc);
+}
+
+// Chunks per loop iteration of the norm pass.  Finding a chunk's data costs two
+// dependent loads (chunk entry -> table row) before the gradient loads can go
+// out; with 8 KiB of bf16 per chunk that chain, not HBM, bounded the kernel.
+// Taking kNormBatch chunks per iteration keeps 4x the bytes in flight per chain.
+constexpr int kNormBatch = 4;
+
+// kCheckEach = false: flag read off the sum (needs inv_scale <= 1); true: per-element test.
+template <bool kBf16, bool kCheckEach>
 __global__ void __launch_bounds__(kBlock)
 norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
             uint32_t nchunks, float inv_scale, double max_norm, int finalize, NormOut out)
 {
-    double acc = 0.0;
+    double acc = 0.0, acc2 = 0.0;  // two chains: halves the DFMA dependency depth
     int bad = 0;
-    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const Chunk ck = chunks[c];
-        const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+    const uint32_t stride = gridDim.x * kNormBatch;
+    for (uint32_t c0 = blockIdx.x * kNormBatch; c0 < nchunks; c0 += stride) {
+        const char *base[kNormBatch];
+        uint32_t nitems[kNormBatch];
+        bool stray = false;  // some chunk of the batch has head / tail / unaligned elements
+#pragma unroll
+        for (int j = 0; j < kNormBatch; ++j) {
+            nitems[j] = 0;
+            base[j] = nullptr;
+            if (c0 + j < nchunks) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                base[j] = (const char *)d.g + cv.item0 * (kBf16 ? 2 : 4);
+                nitems[j] = cv.nitems;
+                stray |= (cv.s_lo1 > cv.s_lo0) | (cv.s_hi1 > cv.s_hi0);
+            }
+        }
         if (kBf16) {
-            const uint16_t *G = (const uint16_t *)d.g;
-            const uint2 *g2 = (const uint2 *)(G + cv.item0);
-            uint2 g[kItemsPerThread];
+            uint2 g[kNormBatch][kItemsPerThread];
 #pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (i < cv.nitems) g[u] = ld_stream(g2 + i);
-            }
+            for (int j = 0; j < kNormBatch; ++j)
 #pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (i < cv.nitems) {
-                    sq_acc(bf16_to_f32(g[u].x & 0xffffu), inv_scale, acc, bad);
-                    sq_acc(bf16_to_f32(g[u].x >> 16), inv_scale, acc, bad);
-                    sq_acc(bf16_to_f32(g[u].y & 0xffffu), inv_scale, acc, bad);
-                    sq_acc(bf16_to_f32(g[u].y >> 16), inv_scale, acc, bad);
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    if (i < nitems[j]) g[j][u] = ld_stream((const uint2 *)base[j] + i);
                 }
-            }
-            for (int r = 0; r < 2; ++r) {
-                uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
-                for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
-                    sq_acc(bf16_to_f32(G[i]), inv_scale, acc, bad);
-            }
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    if (i < nitems[j]) {
+                        sq_acc_fast<kCheckEach>(__uint_as_float(g[j][u].x << 16), inv_scale, acc, bad);
+                        sq_acc_fast<kCheckEach>(__uint_as_float(g[j][u].x & 0xffff0000u), inv_scale, acc2, bad);
+                        sq_acc_fast<kCheckEach>(__uint_as_float(g[j][u].y << 16), inv_scale, acc, bad);
+                        sq_acc_fast<kCheckEach>(__uint_as_float(g[j][u].y & 0xffff0000u), inv_scale, acc2, bad);
+                    }
+                }
         } else {
-            const float *G = (const float *)d.g;
-            const float4 *g4 = (const float4 *)(G + cv.item0);
-            float4 g[kItemsPerThread];
+            float4 g[kNormBatch][kItemsPerThread];
 #pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (i < cv.nitems) g[u] = ld_stream(g4 + i);
-            }
+            for (int j = 0; j < kNormBatch; ++j)
 #pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (i < cv.nitems) {
-                    sq_acc(g[u].x, inv_scale, acc, bad);
-                    sq_acc(g[u].y, inv_scale, acc, bad);
-                    sq_acc(g[u].z, inv_scale, acc, bad);
-                    sq_acc(g[u].w, inv_scale, acc, bad);
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    if (i < nitems[j]) g[j][u] = ld_stream((const float4 *)base[j] + i);
                 }
-            }
-            for (int r = 0; r < 2; ++r) {
-                uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
-                for (uint64_t i = b + threadIdx.x; i < e; i += kBlock)
-                    sq_acc(G[i], inv_scale, acc, bad);
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    if (i < nitems[j]) {
+                        sq_acc_fast<kCheckEach>(g[j][u].x, inv_scale, acc, bad);
+                        sq_acc_fast<kCheckEach>(g[j][u].y, inv_scale, acc2, bad);
+                        sq_acc_fast<kCheckEach>(g[j][u].z, inv_scale, acc, bad);
+                        sq_acc_fast<kCheckEach>(g[j][u].w, inv_scale, acc2, bad);
+                    }
+                }
+        }
+        if (stray) {  // rare: re-derive the views and walk the stray elements one by one
+            for (int j = 0; j < kNormBatch && c0 + j < nchunks; ++j) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                for (int r = 0; r < 2; ++r) {
+                    uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+                    for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                        float gi = kBf16 ? bf16_to_f32(((const uint16_t *)d.g)[i]) : ((const float *)d.g)[i];
+                        sq_acc_fast<kCheckEach>(gi, inv_scale, acc, bad);
+                    }
+                }
             }
         }
     }
+    acc += acc2;
+    if (!kCheckEach) bad = (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN
     double bsum = block_sum_f64(acc, bad);
     __shared__ bool s_last;
     if (threadIdx.x == 0) {
@@ -503,7 +563,7 @@ scale_grads_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         float *G = (float *)d.g;
         float4 *g4 = (float4 *)(G + cv.item0);
         float4 g[kItemsPerThread];
@@ -545,7 +605,7 @@ zero_grads_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict_
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck.index);
+        const ChunkView cv = chunk_view(d, ck);
         if (kBf16) {
             uint16_t *G = (uint16_t *)d.g;
             uint2 *g2 = (uint2 *)(G + cv.item0);

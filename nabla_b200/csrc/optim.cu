@@ -99,8 +99,21 @@ int32_t build_table(nbo_optimizer *h)
         h->groups[g].chunk_begin = (uint32_t)chunks.size();
         for (size_t i = 0; i < np; ++i) {
             if (h->pieces[i].group != (int32_t)g) continue;
-            uint64_t nc = chunks_of(h->pieces[i].n);
-            for (uint64_t c = 0; c < nc; ++c) chunks.push_back(Chunk{(uint32_t)i, (uint32_t)c});
+            const Piece &pc = h->pieces[i];
+            uint64_t nc = chunks_of(pc.n);
+            // the head an aligned row will have: none for separate tensors, the distance to the next
+            // 4-element boundary of the bucket for a piece of a flat bucket
+            uint64_t head = h->zero1 ? ((4 - (pc.bucket_off & 3)) & 3) : 0;
+            if (head > pc.n) head = pc.n;
+            uint64_t body_items = (pc.n - head) >> 2;
+            uint64_t tail = (pc.n - head) & 3;
+            for (uint64_t c = 0; c < nc; ++c) {
+                uint64_t i0 = c * kChunkItems;
+                uint64_t ni = i0 >= body_items ? 0 : (body_items - i0 < kChunkItems ? body_items - i0 : kChunkItems);
+                bool last = (c + 1) * kChunkElems >= pc.n;
+                uint32_t stray = ((c == 0 && head) || (last && tail)) ? 1u : 0u;
+                chunks.push_back(Chunk{(uint32_t)i, (uint32_t)c, (uint32_t)ni, stray});
+            }
         }
         h->groups[g].chunk_end = (uint32_t)chunks.size();
     }

@@ -27,8 +27,11 @@ static_assert(sizeof(TensorDesc) == 56, "TensorDesc layout");
 
 struct Chunk {
     uint32_t tensor;
-    uint32_t index;  // chunk number inside the tensor
+    uint32_t index;   // chunk number inside the tensor
+    uint32_t nitems;  // 4-element items of the aligned body in this chunk (valid while the row is aligned)
+    uint32_t stray;   // 1 when this chunk also owns head or tail elements that are handled one by one
 };
+static_assert(sizeof(Chunk) == 16, "Chunk layout");
 
 // Device-resident decision record written by the norm pass and read by the
 // update pass of the same step, so a skipped step needs no host round trip.

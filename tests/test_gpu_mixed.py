@@ -182,3 +182,30 @@ def test_init_master_from_params_and_zero_grad(nb):
     g = torch.randn(n, device="cuda").to(torch.bfloat16)
     opt.zero_grad([g])
     assert not g.float().abs().sum().item()
+
+
+def test_large_norm_and_exact_flag(nb):
+    """2^25 elements: the norm equals the f64 norm to summation-order noise, a finite value whose square would
+    overflow f32 does not raise the non-finite flag (squares are taken in f64), a true inf / NaN does."""
+    import ctypes as C
+    n = (1 << 25) + 5
+    opt = nb.MixedAdamW.adamw(0.0, 0.0, [(n,)])
+    g = (torch.randn(n, device="cuda") * 3e-3).to(torch.bfloat16)
+
+    def norm(t):
+        a, b = C.c_double(), C.c_int32()
+        opt._h.check(opt._h.lib.nbo_grad_norm(opt._h.h, 1, nb._lib.ptr_array([t.data_ptr()]), C.byref(a), C.byref(b)))
+        return a.value, bool(b.value)
+    want = float(torch.linalg.vector_norm(g.double()))
+    got, bad = norm(g)
+    assert not bad and abs(got - want) <= 1e-12 * want, (got, want)
+    assert norm(g) == (got, bad)                                  # deterministic
+    g[12345] = 1e30                                               # finite; 1e60 overflows f32 but not f64
+    got, bad = norm(g)
+    assert not bad and abs(got - 1e30) <= 1e28
+    for v in (float("inf"), float("nan"), float("-inf")):
+        g[12345] = 0.0
+        g[n - 2] = v
+        assert norm(g)[1] is True
+        g[n - 2] = 0.0
+    assert norm(g)[1] is False
