@@ -162,6 +162,14 @@ NBO_API int32_t nbo_get_lr(const nbo_optimizer *h, int32_t group_id, double *lr)
  * bound list becomes zeros (memset on the stream).  `elem_size` 4 or 2. */
 NBO_API int32_t nbo_zero_grad(nbo_optimizer *h, uint64_t n, void *const *grads);
 
+/* Gradient accumulation, accum[i] = accum[i] + grads[i] elementwise in fp32
+ * (the `buf[i] = &buf[i] + g` loop of Trainer, nabla-train/src/trainer.rs:262-266).
+ * The handle's table holds the accumulation buffers in its parameter column, so
+ * use a handle of its own for this (any group kind; no optimizer state is touched).
+ * Asynchronous. */
+NBO_API int32_t nbo_accumulate_grads(nbo_optimizer *h, uint64_t n, void *const *accum,
+                                     const void *const *grads);
+
 /* ---- OptimState (nabla-train/src/optim/core.rs:64-79) -------------------- */
 
 /* Step count of a group (AdamW::step_count, alg.rs:76-79). */
@@ -324,6 +332,11 @@ NBO_API int32_t nbo_zero1_shard(const nbo_optimizer *h, uint64_t *begin, uint64_
 /* Copies this rank's fp32 state shard to a HOST buffer of shard_elems floats;
  * `which` as in nbo_state_export.  Synchronous. */
 NBO_API int32_t nbo_zero1_state_export(nbo_optimizer *h, int32_t which, float *dst);
+
+/* The reverse: loads this rank's fp32 state shard from a HOST buffer of
+ * shard_elems floats (resume from a checkpoint; OptimState::load_state_tensors,
+ * nabla-train/src/optim/alg.rs:487-518, applied to the slice this rank owns). */
+NBO_API int32_t nbo_zero1_state_import(nbo_optimizer *h, int32_t which, const float *src);
 
 /* ---- introspection ------------------------------------------------------- */
 

@@ -67,6 +67,7 @@ SIGNATURES = {
     "nbo_set_lr": (C.c_int32, [_H, C.c_double]),
     "nbo_get_lr": (C.c_int32, [_H, C.c_int32, _F64P]),
     "nbo_zero_grad": (C.c_int32, [_H, C.c_uint64, _PP]),
+    "nbo_accumulate_grads": (C.c_int32, [_H, C.c_uint64, _PP, _PP]),
     "nbo_step_count": (C.c_int32, [_H, C.c_int32, _U64P]),
     "nbo_set_step_count": (C.c_int32, [_H, C.c_int32, C.c_uint64]),
     "nbo_get_group": (C.c_int32, [_H, C.c_int32, C.POINTER(GroupConfig)]),
@@ -94,6 +95,7 @@ SIGNATURES = {
     "nbo_zero1_step_fused": (C.c_int32, [_H, C.c_int32, C.c_int32, C.c_double, C.POINTER(StepResult)]),
     "nbo_zero1_shard": (C.c_int32, [_H, _U64P, _U64P, _U64P]),
     "nbo_zero1_state_export": (C.c_int32, [_H, C.c_int32, C.c_void_p]),
+    "nbo_zero1_state_import": (C.c_int32, [_H, C.c_int32, C.c_void_p]),
     "nbo_profile": (C.c_int32, [_H, C.c_int32]),
     "nbo_profile_last": (C.c_int32, [_H, _F32P, _F32P]),
     "nbo_launch_count": (C.c_int32, [_H, _U64P]),

@@ -126,6 +126,7 @@ int32_t launch_finalize_ranks(nbo_optimizer *h, const double *gathered, int worl
 int32_t launch_scale_grads(nbo_optimizer *h, int mode, float factor);
 int32_t launch_zero_grads(nbo_optimizer *h, bool bf16);
 int32_t launch_init_master(nbo_optimizer *h);
+int32_t launch_accumulate(nbo_optimizer *h);
 
 // ZeRO-1 fused with its collectives over peer / multicast mappings (transport: 0 local, 1 peer, 2 multicast)
 int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const AdamHP &hp,

@@ -118,6 +118,14 @@ int32_t launch_zero_grads(nbo_optimizer *h, bool bf16)
     return launched(h);
 }
 
+int32_t launch_accumulate(nbo_optimizer *h)
+{
+    if (h->nchunks == 0) return NBO_OK;
+    int grid = grid_for(h, h->nchunks, (const void *)accumulate_kernel);
+    accumulate_kernel<<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks);
+    return launched(h);
+}
+
 int32_t launch_init_master(nbo_optimizer *h)
 {
     if (h->nchunks == 0) return NBO_OK;

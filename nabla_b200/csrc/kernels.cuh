@@ -596,6 +596,41 @@ scale_grads_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict
     }
 }
 
+// Gradient accumulation, buf = buf + g (nabla-train/src/trainer.rs:262-266): the row's `p` column is
+// the accumulation buffer, `g` the fresh gradient.  12 B per element.
+__global__ void __launch_bounds__(kBlock)
+accumulate_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks, uint32_t nchunks)
+{
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Chunk ck = chunks[c];
+        const TensorDesc d = descs[ck.tensor];
+        const ChunkView cv = chunk_view(d, ck);
+        float *A = (float *)d.p;
+        const float *G = (const float *)d.g;
+        float4 *a4 = (float4 *)(A + cv.item0);
+        const float4 *g4 = (const float4 *)(G + cv.item0);
+        float4 a[kItemsPerThread], g[kItemsPerThread];
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) { a[u] = ld_stream(a4 + i); g[u] = ld_stream(g4 + i); }
+        }
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (i < cv.nitems) {
+                a[u].x = __fadd_rn(a[u].x, g[u].x); a[u].y = __fadd_rn(a[u].y, g[u].y);
+                a[u].z = __fadd_rn(a[u].z, g[u].z); a[u].w = __fadd_rn(a[u].w, g[u].w);
+                st_stream(a4 + i, a[u]);
+            }
+        }
+        for (int r = 0; r < 2; ++r) {
+            uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+            for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) A[i] = __fadd_rn(A[i], G[i]);
+        }
+    }
+}
+
 // zero_grad: every gradient element becomes +0 (nabla-ml/src/autograd/ops.rs:1668-1673).
 template <bool kBf16>
 __global__ void __launch_bounds__(kBlock)

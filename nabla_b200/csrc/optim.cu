@@ -602,6 +602,18 @@ int32_t nbo_zero_grad(nbo_optimizer *h, uint64_t n, void *const *grads)
     return launch_zero_grads(h, bf16);
 }
 
+int32_t nbo_accumulate_grads(nbo_optimizer *h, uint64_t n, void *const *accum, const void *const *grads)
+{
+    if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
+    if (n && (!accum || !grads)) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null pointer list");
+    if (h->configured && h->precision != NBO_F32)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: gradient accumulation is defined for fp32 gradients");
+    DeviceGuard guard(h->device);
+    int32_t rc = bind_list(h, n, accum, grads, 4, "accumulate_grads");
+    if (rc != NBO_OK) return rc;
+    return launch_accumulate(h);
+}
+
 int32_t nbo_unscale_and_update(nbo_optimizer *h, uint64_t n, void *const *grads, int32_t *ok)
 {
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");

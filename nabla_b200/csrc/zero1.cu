@@ -386,4 +386,16 @@ int32_t nbo_zero1_state_export(nbo_optimizer *h, int32_t which, float *dst)
     return NBO_OK;
 }
 
+int32_t nbo_zero1_state_import(nbo_optimizer *h, int32_t which, const float *src)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    float *base = which == 0 ? h->d_s0 : which == 1 ? h->d_s1 : which == 2 ? h->d_s2 : nullptr;
+    if (!base || !src) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: bad state selector or null buffer");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    NBO_CUDA(h, cudaMemcpyAsync(base, src, h->zero1->shard * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    return NBO_OK;
+}
+
 }  // extern "C"

@@ -68,6 +68,7 @@ class Zero1AdamW:
                  unique_id: Optional[bytes] = None, *, device=None, stream=None):
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
+        self._configs, self._gid_of = kept, gid_of
         self.total = sum(self._numel)
         self.rank, self.world = rank, world
         self.shard, self.padded = geometry(self.total, world)
@@ -158,6 +159,64 @@ class Zero1AdamW:
         out = torch.empty(self.shard, dtype=torch.float32)
         self._h.check(self._h.lib.nbo_zero1_state_export(self._h.h, which, C.c_void_p(out.data_ptr())))
         return out
+
+    def load_state_shard(self, which: int, values: torch.Tensor) -> None:
+        v = values.detach().to("cpu", torch.float32).contiguous()
+        if v.numel() != self.shard:
+            raise ValueError(f"expected {self.shard} floats for this rank's shard")
+        self._h.check(self._h.lib.nbo_zero1_state_import(self._h.h, which, C.c_void_p(v.data_ptr())))
+
+    # ---- checkpoint: stitch the shards back into the reference's per-tensor state names ----------
+    def state_tensors(self, group=None):
+        """On rank 0: [(name, tensor)] with the names a GroupOptimizer uses (g{k}.m{i} / g{k}.v{i}) plus the
+        fp32 masters as g{k}.w{i}; None on the other ranks.  The shards travel through the host."""
+        full = []
+        for which in (0, 1, 2):
+            shard = self.state_shard(which)
+            if self.world == 1:
+                full.append(shard[:self.total])
+                continue
+            import torch.distributed as dist
+            parts = [None] * self.world if self.rank == 0 else None
+            dist.gather_object(shard, parts, dst=0, group=group)
+            full.append(torch.cat(parts)[:self.total] if self.rank == 0 else None)
+        if self.rank != 0:
+            return None
+        offs, out = [0], []
+        for n in self._numel:
+            offs.append(offs[-1] + n)
+        for gi in range(len(self._configs)):
+            idx = [i for i, g in enumerate(self._gid_of) if g == gi]
+            for which, p in ((0, "m"), (1, "v"), (2, "w")):
+                for li, i in enumerate(idx):
+                    out.append((f"g{gi}.{p}{li}", full[which][offs[i]:offs[i + 1]].clone()))
+        return out
+
+    def load_state_tensors(self, tensors) -> None:
+        """Every rank passes the full per-tensor list (as loaded from optim.nbla) and keeps its own slice."""
+        offs = [0]
+        for n in self._numel:
+            offs.append(offs[-1] + n)
+        byname = {n: torch.as_tensor(t, dtype=torch.float32).reshape(-1) for n, t in tensors}
+        b = self.rank * self.shard
+        for which, p in ((0, "m"), (1, "v"), (2, "w")):
+            flat = torch.zeros(self.padded, dtype=torch.float32)
+            for gi in range(len(self._configs)):
+                idx = [i for i, g in enumerate(self._gid_of) if g == gi]
+                for li, i in enumerate(idx):
+                    key = f"g{gi}.{p}{li}"
+                    if key not in byname:
+                        raise ValueError(f"missing {p}{li}")
+                    flat[offs[i]:offs[i + 1]] = byname[key]
+            self.load_state_shard(which, flat[b:b + self.shard])
+
+    def scaler_state(self) -> L.ScalerState:
+        st = L.ScalerState()
+        self._h.check(self._h.lib.nbo_scaler_get(self._h.h, C.byref(st)))
+        return st
+
+    def load_scaler_state(self, st: L.ScalerState) -> None:
+        self._h.check(self._h.lib.nbo_scaler_set(self._h.h, C.byref(st)))
 
     def set_lr(self, lr: float) -> None:
         self._h.check(self._h.lib.nbo_set_lr(self._h.h, float(lr)))

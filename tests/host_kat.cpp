@@ -1,0 +1,95 @@
+// The reference's own optimizer tests (nabla-train/tests/optim.rs:47-165, tests/trainer.rs:171-203),
+// written against the C++ host mirror, in f32 on the GPU.  Prints HOST_KAT_OK on success.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cuda_runtime.h>
+
+#include "../nabla_b200/host/nabla_optim.hpp"
+
+using namespace nabla_b200;
+
+#define REQUIRE(c)                                                        \
+    do {                                                                  \
+        if (!(c)) { std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #c); std::exit(1); } \
+    } while (0)
+
+static Tensor mat(float v)
+{
+    Tensor t; t.rows = t.cols = 1;
+    REQUIRE(cudaMalloc(&t.device_ptr, sizeof(float)) == cudaSuccess);
+    REQUIRE(cudaMemcpy(t.device_ptr, &v, sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess);
+    return t;
+}
+static float get(const Tensor &t)
+{
+    float v;
+    REQUIRE(cudaMemcpy(&v, t.device_ptr, sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess);
+    return v;
+}
+
+int main()
+{
+    {   // sgd_step_updates_param
+        Tensor param = mat(1.0f), grad = mat(1.0f);
+        Sgd opt(0.1, {{1, 1}});
+        opt.step({&param}, {&grad});
+        REQUIRE(std::fabs(get(param) - 0.9f) < 1e-6f);
+    }
+    {   // adam_step_updates_param / adamw_step_updates_param
+        Tensor p1 = mat(1.0f), p2 = mat(1.0f), grad = mat(1.0f);
+        Adam a(0.1, {{1, 1}});
+        AdamW w(0.1, {{1, 1}});
+        a.step({&p1}, {&grad});
+        w.step({&p2}, {&grad});
+        REQUIRE(get(p1) < 1.0f && get(p2) < 1.0f && get(p2) < get(p1));
+        REQUIRE(a.step_count() == 1);
+    }
+    {   // schedules
+        REQUIRE(std::fabs(lr_at_step(LrSchedule::Linear(0, 10), 1.0, 0) - 1.0) < 1e-10);
+        REQUIRE(lr_at_step(LrSchedule::Linear(0, 10), 1.0, 10) <= 1e-10);
+        auto st = LrSchedule::Step(2, 0.1);
+        REQUIRE(std::fabs(lr_at_step(st, 1.0, 0) - 1.0) < 1e-10);
+        REQUIRE(std::fabs(lr_at_step(st, 1.0, 2) - 0.1) < 1e-10);
+        REQUIRE(std::fabs(lr_at_step(st, 1.0, 4) - 0.01) < 1e-10);
+        REQUIRE(lr_at_step(LrSchedule::OneCycle(1.0, 10, 0.5), 0.1, 3) > 0.1);
+    }
+    {   // grad_scaler_unscale / grad_scaler_detects_inf
+        std::vector<Tensor> g{mat(2.0f)};
+        GradScaler sc({{1, 1}});
+        REQUIRE(sc.unscale_and_update(g));
+        REQUIRE(get(g[0]) < 2.0f && get(g[0]) == 2.0f / 65536.0f);
+        std::vector<Tensor> bad{mat(INFINITY)};
+        GradScaler sc2({{1, 1}});
+        REQUIRE(!sc2.unscale_and_update(bad));
+        REQUIRE(std::fabs(get(bad[0])) < 1e-12f && sc2.scale_factor() == 32768.0);
+    }
+    {   // group_optimizer_weight_decay_exclusion
+        Tensor weight = mat(2.0f), bias = mat(3.0f), z1 = mat(0.0f), z2 = mat(0.0f);
+        auto bias_group = ParamGroupConfig::sgd("no_decay", ParamSelector::Any({{ParamMatch::Suffix, "bias"}}), 1.0, 0.0, 0.0);
+        auto decay_group = ParamGroupConfig::sgd("decay", ParamSelector::All(), 1.0, 0.0, 0.1);
+        GroupOptimizer opt({{"weight", &weight}, {"bias", &bias}}, {bias_group}, &decay_group);
+        REQUIRE(opt.groups() == 2);
+        opt.step({&weight, &bias}, {&z1, &z2});
+        REQUIRE(std::fabs(get(weight) - 1.8f) < 1e-6f);
+        REQUIRE(get(bias) == 3.0f);
+    }
+    {   // clip_grad_norm_scales
+        std::vector<Tensor> grads{mat(3.0f), mat(4.0f)};
+        double reported = clip_grad_norm(grads, 2.5);
+        double after = std::sqrt((double)get(grads[0]) * get(grads[0]) + (double)get(grads[1]) * get(grads[1]));
+        REQUIRE(reported == 5.0 && std::fabs(after - 2.5) < 1e-6);
+        REQUIRE(clip_grad_norm(grads, 0.0) == 0.0);
+    }
+    {   // length mismatches carry the reference's panic text
+        Tensor p = mat(1.0f), g = mat(1.0f);
+        AdamW opt(0.1, {{1, 1}, {1, 1}});
+        bool threw = false;
+        try { opt.step({&p}, {&g}); } catch (const std::logic_error &e) {
+            threw = std::string(e.what()) == "nabla-train: AdamW params count mismatch";
+        }
+        REQUIRE(threw);
+    }
+    std::printf("HOST_KAT_OK\n");
+    return 0;
+}
