@@ -199,10 +199,10 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
                 if (kIn != kLocal) st_stream(g2 + i, g[u]);
-                mixed_elem(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
+                mixed_elem<true>(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
+                mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
+                mixed_elem<true>(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
+                mixed_elem<true>(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
                 uint2 o;
                 o.x = f32_to_bf16(w[u].x) | (f32_to_bf16(w[u].y) << 16);
                 o.y = f32_to_bf16(w[u].z) | (f32_to_bf16(w[u].w) << 16);
@@ -217,7 +217,7 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
                 uint16_t gi = kIn == kLocal ? G[i] : reduce_elem(G + i, pa);
                 if (kIn != kLocal) G[i] = gi;
-                mixed_elem(bf16_to_f32(gi), d.s2[i], d.s0[i], d.s1[i], hp, clip);
+                mixed_elem<true>(bf16_to_f32(gi), d.s2[i], d.s0[i], d.s1[i], hp, clip);
                 publish_elem(P + i, (uint16_t)f32_to_bf16(d.s2[i]), pa);
             }
         }

@@ -60,9 +60,14 @@ int32_t launch_sgd_f32(nbo_optimizer *h, uint32_t cb, uint32_t nc, const SgdHP &
 int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl)
 {
     if (nc == 0) return NBO_OK;
-    int grid = grid_for(h, nc, (const void *)adam_mixed_kernel);
-    adam_mixed_kernel<<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp,
-                                                      with_ctrl ? h->d_ctrl : nullptr);
+    if (with_ctrl || hp.inv_scale != 1.0f) {
+        int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<true>);
+        adam_mixed_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp,
+                                                                with_ctrl ? h->d_ctrl : nullptr);
+    } else {
+        int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<false>);
+        adam_mixed_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp, nullptr);
+    }
     return launched(h);
 }
 

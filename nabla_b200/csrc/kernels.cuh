@@ -63,7 +63,7 @@ __device__ __forceinline__ void adam_elem(float &p, float g, float &m, float &v,
     float pp = p;
     if (h.decoupled)
         pp = __fmul_rn(pp, h.decay);
-    pp = __fadd_rn(pp, __fmul_rn(-1.0f, u));
+    pp = __fsub_rn(pp, u);  // p + (-1 * u): the product is an exact negation, so one subtraction rounds the same
     p = pp;
     m = mm;
     v = vv;
@@ -237,20 +237,71 @@ sgd_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ c
 // 14 B per element.  Returns at once when the norm pass flagged the step as
 // skipped.
 
+template <bool kScaled>
 __device__ __forceinline__ void mixed_elem(float g, float &w, float &m, float &v, const AdamHP &hp,
                                            float clip)
 {
-    g = __fmul_rn(g, hp.inv_scale);
-    g = __fmul_rn(g, clip);
+    if (kScaled) {  // x * 1.0f is exact, so the unscaled / unclipped step skips both multiplies
+        g = __fmul_rn(g, hp.inv_scale);
+        g = __fmul_rn(g, clip);
+    }
     adam_elem(w, g, m, v, hp);
 }
 
+// Two fp32 -> one bf16x2 word.  The hardware convert is round-to-nearest-even for every non-NaN input
+// (infinities, subnormals and the round-up-to-infinity case included) but canonicalises NaNs, so NaNs take
+// the integer path that keeps their sign and upper payload as the reference's cast does.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    if (lo != lo || hi != hi) d = f32_to_bf16(lo) | (f32_to_bf16(hi) << 16);
+    return d;
+}
+
+template <bool kFull, bool kScaled>
+__device__ __forceinline__ void mixed_items(uint2 *p2, const uint2 *g2, float4 *w4, float4 *m4, float4 *v4,
+                                            uint32_t nitems, const AdamHP &hp, float clip)
+{
+    uint2 g[kItemsPerThread];
+    float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+#pragma unroll
+    for (int u = 0; u < kItemsPerThread; ++u) {
+        uint32_t i = threadIdx.x + u * kBlock;
+        if (kFull || i < nitems) {
+            g[u] = ld_stream(g2 + i);
+            w[u] = ld_stream(w4 + i);
+            m[u] = ld_stream(m4 + i);
+            v[u] = ld_stream(v4 + i);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kItemsPerThread; ++u) {
+        uint32_t i = threadIdx.x + u * kBlock;
+        if (kFull || i < nitems) {
+            mixed_elem<kScaled>(__uint_as_float(g[u].x << 16), w[u].x, m[u].x, v[u].x, hp, clip);
+            mixed_elem<kScaled>(__uint_as_float(g[u].x & 0xffff0000u), w[u].y, m[u].y, v[u].y, hp, clip);
+            mixed_elem<kScaled>(__uint_as_float(g[u].y << 16), w[u].z, m[u].z, v[u].z, hp, clip);
+            mixed_elem<kScaled>(__uint_as_float(g[u].y & 0xffff0000u), w[u].w, m[u].w, v[u].w, hp, clip);
+            uint2 o;
+            o.x = pack_bf16x2(w[u].x, w[u].y);
+            o.y = pack_bf16x2(w[u].z, w[u].w);
+            st_stream(w4 + i, w[u]);
+            st_stream(m4 + i, m[u]);
+            st_stream(v4 + i, v[u]);
+            st_stream(p2 + i, o);
+        }
+    }
+}
+
+// kScaled = false is the plain step (no loss scale, no clipping, no decision record).
+template <bool kScaled>
 __global__ void __launch_bounds__(kBlock)
 adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
                   uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl)
 {
     float clip = 1.0f;
-    if (ctrl != nullptr) {
+    if (kScaled && ctrl != nullptr) {
         if (ctrl->skip)
             return;
         clip = ctrl->clip_scale;
@@ -266,40 +317,11 @@ adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict_
         float4 *m4 = (float4 *)(d.s0 + cv.item0);
         float4 *v4 = (float4 *)(d.s1 + cv.item0);
         float4 *w4 = (float4 *)(d.s2 + cv.item0);
-
-        uint2 g[kItemsPerThread];
-        float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                g[u] = ld_stream(g2 + i);
-                w[u] = ld_stream(w4 + i);
-                m[u] = ld_stream(m4 + i);
-                v[u] = ld_stream(v4 + i);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                mixed_elem(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
-                mixed_elem(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
-                uint2 o;
-                o.x = f32_to_bf16(w[u].x) | (f32_to_bf16(w[u].y) << 16);
-                o.y = f32_to_bf16(w[u].z) | (f32_to_bf16(w[u].w) << 16);
-                st_stream(w4 + i, w[u]);
-                st_stream(m4 + i, m[u]);
-                st_stream(v4 + i, v[u]);
-                st_stream(p2 + i, o);
-            }
-        }
+        mixed_items<false, kScaled>(p2, g2, w4, m4, v4, cv.nitems, hp, clip);
         for (int r = 0; r < 2; ++r) {
             uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
             for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
-                mixed_elem(bf16_to_f32(G[i]), d.s2[i], d.s0[i], d.s1[i], hp, clip);
+                mixed_elem<kScaled>(bf16_to_f32(G[i]), d.s2[i], d.s0[i], d.s1[i], hp, clip);
                 P[i] = (uint16_t)f32_to_bf16(d.s2[i]);
             }
         }

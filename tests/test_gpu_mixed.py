@@ -171,6 +171,18 @@ def test_bf16_cast_edge_values_through_the_kernel(nb, oracle):
     oracle.adam_step(want_w, np.zeros(n, np.float32), m, v, 0.0, weight_decay=0.0, step=1, decoupled=True)
     assert np.array_equal(bits(got_w), bits(want_w))
     assert np.array_equal(bf16_bits(p), oracle.bf16_from_f32(want_w))
+    # NaN masters: the arithmetic canonicalises NaNs differently on the two machines, but the cast of whatever
+    # master the GPU holds keeps sign and upper payload with the quiet bit set, exactly like the oracle's cast
+    nan_bits = np.array([0x7FC00000, 0xFFC00001, 0x7F800001, 0xFFFFFFFF, 0x7FABCDEF, 0x3F800000, 0x7F800000],
+                        dtype=np.uint32)
+    wn = np.tile(nan_bits, 600).view(np.float32)
+    opt2 = nb.MixedAdamW.adamw(0.0, 0.0, [(wn.size,)])
+    opt2.load_master(0, torch.from_numpy(wn.copy()))
+    p2 = torch.zeros(wn.size, dtype=torch.bfloat16, device="cuda")
+    opt2.step([p2], [torch.zeros_like(p2)], use_scaler=False, max_norm=0.0)
+    gw = opt2.master(0).numpy()
+    assert np.isnan(gw).sum() == 5 * 600
+    assert np.array_equal(bf16_bits(p2), oracle.bf16_from_f32(gw))
 
 
 def test_init_master_from_params_and_zero_grad(nb):
