@@ -84,6 +84,10 @@ WORKLOADS = {
                        desc="10,000 fp32 tensors log-uniform in [1, 2^20], AdamW"),
     "frag_sgdm": dict(kind="f32", opt="sgdm", shapes=frag_sizes, lr=0.1, bytes_per_elem=20,
                       desc="10,000 fp32 tensors log-uniform in [1, 2^20], SGD momentum 0.9"),
+    "one_adamw": dict(kind="f32", opt="adamw", shapes=lambda: [(sum(n for (n,) in frag_sizes()),)], lr=1e-3, wd=0.01,
+                      bytes_per_elem=28, desc="the frag list's elements as ONE fp32 tensor, AdamW (roofline reference)"),
+    "one_sgdm": dict(kind="f32", opt="sgdm", shapes=lambda: [(sum(n for (n,) in frag_sizes()),)], lr=0.1,
+                     bytes_per_elem=20, desc="the frag list's elements as ONE fp32 tensor, SGD momentum 0.9"),
     "mlp_sgd": dict(kind="f32", opt="sgd", shapes=lambda: [(256, 784), (256,), (128, 256), (128,), (10, 128), (10,)],
                     lr=0.01, bytes_per_elem=12, desc="MLP 784-256-128-10 fp32 SGD"),
 }

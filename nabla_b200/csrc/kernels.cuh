@@ -58,8 +58,19 @@ __device__ __forceinline__ void adam_elem(float &p, float g, float &m, float &v,
     float vv = __fmul_rn(v, h.b2);
     float gs = __fmul_rn(g, g);
     vv = __fadd_rn(vv, __fmul_rn(h.one_minus_b2, gs));
-    float den = __fadd_rn(__fsqrt_rn(__fmul_rn(vv, h.inv_bc2)), h.eps);
-    float u = __fdiv_rn(__fmul_rn(mm, h.ss), den);
+    // Correctly rounded sqrt and divide branch to a slow routine when an operand is zero; a parameter
+    // that never received a gradient has g = m = v = 0 on every step, and whole rows of them (unused
+    // embedding entries) would run the update a quarter slower.  Both zero cases have exact, trivial
+    // answers (sqrt(+0) = +0; 0 / d = 0 for d > 0, sign kept), so they are answered by a select and the
+    // routines only ever see non-zero operands.
+    float t = __fmul_rn(vv, h.inv_bc2);
+    bool tz = t == 0.0f;
+    float rt = __fsqrt_rn(tz ? 1.0f : t);
+    float den = __fadd_rn(tz ? t : rt, h.eps);
+    float a = __fmul_rn(mm, h.ss);
+    bool az = a == 0.0f && den > 0.0f;
+    float q = __fdiv_rn(az ? den : a, den);
+    float u = az ? a : q;
     float pp = p;
     if (h.decoupled)
         pp = __fmul_rn(pp, h.decay);

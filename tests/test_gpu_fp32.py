@@ -405,3 +405,29 @@ def test_error_behaviour(nb):
     # after all those refusals the handle still works
     opt.step(p, [torch.ones(4, device="cuda") for _ in range(2)])
     assert opt.step_count() == 1 and float(p[0][0]) < 0
+
+
+def test_untouched_parameters_and_zero_eps(nb, oracle):
+    """g = m = v = 0 (a parameter that never received a gradient) takes the select path around the sqrt and the
+    divide: the result must still be the reference's (decay only), -0 gradients included; with eps = 0 the
+    reference's 0/0 = NaN must come out too."""
+    n = 5000
+    rng = np.random.default_rng(12)
+    p = rng.normal(0, 1, n).astype(np.float32)
+    g = np.zeros(n, np.float32)
+    g[::7] = -0.0
+    g[1::3] = rng.normal(0, 1e-3, len(g[1::3])).astype(np.float32)      # a mix of touched and untouched
+    for eps in (1e-8, 0.0):
+        dp, dg = dev(p), dev(g)
+        opt = nb.AdamW(1e-2, [(n,)]).weight_decay(0.1).eps(eps)
+        po, m, v = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        for t in range(1, 4):
+            opt.step([dp], [dg])
+            oracle.adam_step(po, g, m, v, 1e-2, eps=eps, weight_decay=0.1, step=t, decoupled=True)
+        got = host(dp)
+        assert np.array_equal(np.isnan(got), np.isnan(po))
+        assert np.isnan(po).any() == (eps == 0.0)
+        ok = ~np.isnan(po)
+        assert_close_rel(got[ok], po[ok], f"eps={eps}")
+        untouched = (g == 0) & ok
+        assert np.array_equal(bits(got[untouched]), bits(po[untouched]))      # decay only: exact
