@@ -196,7 +196,7 @@ def cpu_reference_step_time(sample_elems, steps, warmup, mixed=True):
     return (time.perf_counter() - t0) / max(steps, 1), cores
 
 
-def calibrated_cpu_sample(target_seconds, mixed=True, cap=1 << 27):
+def calibrated_cpu_sample(target_seconds, mixed=True, cap=1 << 29):
     probe = 1 << 23
     t, _ = cpu_reference_step_time(probe, 1, 1, mixed)
     n = int(probe * target_seconds / max(t, 1e-6))
