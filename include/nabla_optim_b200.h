@@ -149,6 +149,15 @@ NBO_API int32_t nbo_set_tensors(nbo_optimizer *h, uint64_t n, const uint64_t *nu
 NBO_API int32_t nbo_step(nbo_optimizer *h, uint64_t n, void *const *params,
                          const void *const *grads);
 
+/* adamw_step (alg.rs:431-469): AdamW on ONE fp32 tensor whose moments `m` and `v`
+ * are owned by the caller (device pointers, n floats each); `step` is the
+ * 1-based step number used for the bias corrections.  Needs no handle and
+ * allocates nothing: the tensor description travels in the kernel arguments.
+ * Asynchronous on `stream`. */
+NBO_API int32_t nbo_adamw_step(int32_t device, void *stream, void *param, const void *grad, float *m,
+                               float *v, uint64_t n, double lr, double beta1, double beta2, double eps,
+                               double weight_decay, uint64_t step);
+
 /* Optimizer::reset: zero the state and the Adam step counts (alg.rs:152-162). */
 NBO_API int32_t nbo_reset(nbo_optimizer *h);
 

@@ -5,7 +5,7 @@ this package is the Python host mirror of the reference's Rust interface on top 
 """
 from .optim import (Adam, AdamW, GradClipper, GradScaler, GroupOptimizer, LrSchedule, MixedAdamW,
                     Optimizer, ParamExclusionPreset, ParamGroupConfig, ParamMatch, ParamSelector, Sgd,
-                    StepOutcome, assign_groups, clip_grad_norm, lr_at_step)
+                    StepOutcome, adamw_step, assign_groups, clip_grad_norm, lr_at_step)
 from . import checkpoint
 from .trainer import GradAccumulator, GradNanPolicy, NonFiniteGradient, TrainerTail
 from .zero1 import Zero1AdamW, exchange_unique_id, geometry, shard_pieces
@@ -13,6 +13,6 @@ from .zero1 import Zero1AdamW, exchange_unique_id, geometry, shard_pieces
 __all__ = [
     "Adam", "AdamW", "GradAccumulator", "GradClipper", "GradNanPolicy", "NonFiniteGradient", "TrainerTail", "GradScaler", "GroupOptimizer", "LrSchedule", "MixedAdamW", "Optimizer",
     "ParamExclusionPreset", "ParamGroupConfig", "ParamMatch", "ParamSelector", "Sgd", "StepOutcome",
-    "Zero1AdamW", "assign_groups", "clip_grad_norm", "exchange_unique_id", "geometry", "lr_at_step",
+    "Zero1AdamW", "adamw_step", "assign_groups", "clip_grad_norm", "exchange_unique_id", "geometry", "lr_at_step",
     "shard_pieces",
 ]

@@ -63,6 +63,8 @@ SIGNATURES = {
     "nbo_add_group": (C.c_int32, [_H, C.POINTER(GroupConfig), _I32P]),
     "nbo_set_tensors": (C.c_int32, [_H, C.c_uint64, _U64P, _I32P, C.c_int32]),
     "nbo_step": (C.c_int32, [_H, C.c_uint64, _PP, _PP]),
+    "nbo_adamw_step": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64,
+                                   C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, C.c_uint64]),
     "nbo_reset": (C.c_int32, [_H]),
     "nbo_set_lr": (C.c_int32, [_H, C.c_double]),
     "nbo_get_lr": (C.c_int32, [_H, C.c_int32, _F64P]),

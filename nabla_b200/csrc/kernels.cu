@@ -2,6 +2,7 @@
 // host code calls.  Grids are persistent: SM count x resident CTAs per SM
 // (from the occupancy calculator), capped by the number of chunks.
 #include <map>
+#include <mutex>
 
 #include "internal.h"
 #include "kernels.cuh"
@@ -12,6 +13,8 @@ namespace nbo {
 static int grid_for(const nbo_optimizer *h, uint32_t nchunks, const void *kernel)
 {
     static std::map<const void *, int> cache;  // resident CTAs per SM, per kernel
+    static std::mutex cache_lock;               // handles may be driven from different host threads
+    std::lock_guard<std::mutex> guard(cache_lock);
     int per_sm;
     auto it = cache.find(kernel);
     if (it == cache.end()) {
@@ -140,6 +143,46 @@ int32_t launch_init_master(nbo_optimizer *h)
 }
 
 }  // namespace nbo
+
+// ---- adamw_step: one tensor, caller-owned moments, no handle ---------------------------------------
+
+extern "C" int32_t nbo_adamw_step(int32_t device, void *stream, void *param, const void *grad, float *m,
+                                  float *v, uint64_t n, double lr, double beta1, double beta2, double eps,
+                                  double weight_decay, uint64_t step)
+{
+    using namespace nbo;
+    if (n == 0) return NBO_OK;
+    if (!param || !grad || !m || !v)
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_adamw_step: null device pointer");
+    uintptr_t all = (uintptr_t)param | (uintptr_t)grad | (uintptr_t)m | (uintptr_t)v;
+    if (all & 3u) return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_adamw_step: pointer not aligned to f32");
+    if (n > (uint64_t)0xfffffff0u * kChunkElems)
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_adamw_step: tensor too large");
+    int prev = -1;
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail_cuda(nullptr, e, "cudaSetDevice");
+    nbo_group_config cfg{NBO_ADAMW, lr, beta1, beta2, eps, weight_decay, 0.0};
+    AdamHP hp = adam_hparams(cfg, step, 1.0f);
+    TensorDesc d;
+    d.p = param; d.g = grad; d.s0 = m; d.s1 = v; d.s2 = nullptr; d.n = n; d.group = 0;
+    d.head = (all & 15u) ? 0xffffffffu : 0u;
+    uint32_t nchunks = (uint32_t)((n + kChunkElems - 1) / kChunkElems);
+    int sms = 0, per_sm = 0;
+    int32_t rc = [&]() -> int32_t {
+        NBO_CUDA(nullptr, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void *)adam_f32_single_kernel, kBlock, 0) !=
+                cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        long long grid = (long long)sms * per_sm;
+        if (grid > (long long)nchunks) grid = nchunks;
+        adam_f32_single_kernel<<<(int)grid, kBlock, 0, (cudaStream_t)stream>>>(d, nchunks, hp);
+        NBO_CUDA(nullptr, cudaGetLastError());
+        return NBO_OK;
+    }();
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    return rc;
+}
 
 // ---- ZeRO-1 fused with its collectives (fused_nvlink.cuh) ------------------------------------
 
@@ -272,7 +315,9 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
     cudaError_t e = cudaGetDevice(&prev);
     if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
     if (e != cudaSuccess) return fail_cuda(nullptr, e, "cudaSetDevice");
+    static std::mutex setup_lock;  // guards the per-device address cache, not the scratch itself
     int32_t rc = [&]() -> int32_t {
+        std::lock_guard<std::mutex> guard(setup_lock);
         if (!scratch_of[device]) {
             // The array's name is only a host-side stand-in: ask the runtime for its address on THIS device.
             void *p = nullptr;

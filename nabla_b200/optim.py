@@ -321,6 +321,19 @@ class Sgd(_Single):
             self._h.state_import(i, 0, t.reshape(-1))
 
 
+def adamw_step(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, lr: float, beta1: float,
+               beta2: float, eps: float, weight_decay: float, step: int) -> None:
+    """``adamw_step`` (nabla-train/src/optim/alg.rs:431-469): AdamW on one tensor with caller-owned m and v."""
+    _check_tensors([param, grad, m, v], torch.float32, "adamw_step")
+    n = param.numel()
+    if not (grad.numel() == m.numel() == v.numel() == n):
+        raise AssertionError("nabla: axpy_inplace shapes must match")
+    stream = torch.cuda.current_stream(param.device).cuda_stream
+    L.check(None, L.load().nbo_adamw_step(param.device.index, C.c_void_p(stream), C.c_void_p(param.data_ptr()),
+                                          C.c_void_p(grad.data_ptr()), C.c_void_p(m.data_ptr()),
+                                          C.c_void_p(v.data_ptr()), n, lr, beta1, beta2, eps, weight_decay, step))
+
+
 # --------------------------------------------------------------------------- param groups
 
 @dataclass

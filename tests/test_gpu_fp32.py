@@ -431,3 +431,22 @@ def test_untouched_parameters_and_zero_eps(nb, oracle):
         assert_close_rel(got[ok], po[ok], f"eps={eps}")
         untouched = (g == 0) & ok
         assert np.array_equal(bits(got[untouched]), bits(po[untouched]))      # decay only: exact
+
+
+@pytest.mark.parametrize("n", [1, 5, 4097, 3 * 4096 + 2, 1 << 20])
+def test_adamw_step_free_function(nb, oracle, n):
+    """adamw_step (alg.rs:431-469): one tensor, caller-owned m and v, explicit step number; aligned and not."""
+    rng = np.random.default_rng(n)
+    for off in (0, 1):
+        p = rng.normal(0, 0.02, n).astype(np.float32); m = np.zeros(n, np.float32); v = np.zeros(n, np.float32)
+        base = [torch.zeros(n + 8, device="cuda") for _ in range(4)]
+        dp, dg, dm, dv = [b[off:off + n] for b in base]
+        dp.copy_(torch.from_numpy(p))
+        for t in range(1, 4):
+            g = rng.normal(0, 1e-3, n).astype(np.float32)
+            dg.copy_(torch.from_numpy(g))
+            nb.adamw_step(dp, dg, dm, dv, 1e-3, 0.9, 0.999, 1e-8, 0.05, t)
+            oracle.adam_step(p, g, m, v, 1e-3, weight_decay=0.05, step=t, decoupled=True)
+        assert np.array_equal(bits(dm), bits(m)) and np.array_equal(bits(dv), bits(v))
+        assert_close_rel(dp, p, f"n={n} off={off}")
+        assert not base[0][off + n:].any() and not base[2][:off].any()       # nothing outside the tensor is touched
