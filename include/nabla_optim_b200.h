@@ -267,6 +267,26 @@ NBO_API int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params
                                const void *const *grads_bf16, int32_t use_scaler,
                                double max_norm, nbo_step_result *result);
 
+/* The same step without any host round trip, for callers that keep the GPU fed
+ * (or capture the optimizer phase into a CUDA graph): step counters, bias
+ * corrections and the GradScaler bookkeeping are computed on the device from a
+ * device-resident copy of the state, so nothing is read back and every launch
+ * has constant arguments.  A skipped step is decided and accounted for on the
+ * device (trainer.rs:230-237).  Up to 32 groups; unsharded handles only.
+ * The host-side view (nbo_step_count, nbo_scaler_get, nbo_get_lr ...) is
+ * brought up to date by any of those calls or by nbo_step_mixed_collect, each
+ * of which synchronises the stream; host-side changes (nbo_set_lr,
+ * nbo_scaler_set ...) are sent down again by the next asynchronous step.
+ * Arithmetic and results are identical to nbo_step_mixed. */
+NBO_API int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
+                                     const void *const *grads_bf16, int32_t use_scaler,
+                                     double max_norm);
+
+/* Outcome of the most recent asynchronous step (and the number of such steps
+ * the device has completed since the last hand-over).  Synchronises. */
+NBO_API int32_t nbo_step_mixed_collect(nbo_optimizer *h, nbo_step_result *result,
+                                       uint64_t *steps_enqueued);
+
 /* ---- LR schedules (pure host math) --------------------------------------- */
 
 /* lr_at_step (nabla-train/src/optim/core.rs:130-173); `step` is the trainer's

@@ -85,6 +85,8 @@ SIGNATURES = {
                                           C.c_void_p]),
     "nbo_init_master_from_params": (C.c_int32, [_H, C.c_uint64, _PP]),
     "nbo_step_mixed": (C.c_int32, [_H, C.c_uint64, _PP, _PP, C.c_int32, C.c_double, C.POINTER(StepResult)]),
+    "nbo_step_mixed_async": (C.c_int32, [_H, C.c_uint64, _PP, _PP, C.c_int32, C.c_double]),
+    "nbo_step_mixed_collect": (C.c_int32, [_H, C.POINTER(StepResult), _U64P]),
     "nbo_lr_at_step": (C.c_int32, [C.POINTER(LrScheduleC), C.c_double, C.c_uint64, _F64P]),
     "nbo_zero1_unique_id": (C.c_int32, [C.c_void_p]),
     "nbo_zero1_geometry": (C.c_int32, [C.c_uint64, C.c_int32, _U64P, _U64P]),

@@ -78,6 +78,15 @@ struct nbo_optimizer {
     bool prof_norm_valid = false, prof_update_valid = false;
     cudaEvent_t prof_ev[4] = {nullptr, nullptr, nullptr, nullptr};
 
+    // device-resident state of the asynchronous step; `dev_newer` = the device copy has advanced past the
+    // host mirrors (groups[].step_count, scaler) and must be collected before the host reads or changes them
+    nbo::DevState *d_state = nullptr;
+    nbo::DevState *h_state = nullptr;  // pinned
+    nbo::AdamHP *d_hp = nullptr;       // [kMaxDevGroups]
+    float *d_inv_scale = nullptr;
+    bool dev_newer = false;
+    int last_async_checked = 0;
+
     nbo_scaler_state scaler{65536.0, 2.0, 0.5, 2000, 0};
     uint64_t launches = 0;
 
@@ -127,6 +136,13 @@ int32_t launch_scale_grads(nbo_optimizer *h, int mode, float factor);
 int32_t launch_zero_grads(nbo_optimizer *h, bool bf16);
 int32_t launch_init_master(nbo_optimizer *h);
 int32_t launch_accumulate(nbo_optimizer *h);
+int32_t launch_norm_dev(nbo_optimizer *h, const float *inv_scale_dev, double max_norm);
+int32_t launch_prepare(nbo_optimizer *h, int use_scaler);
+int32_t launch_commit(nbo_optimizer *h, bool checked, int use_scaler);
+int32_t launch_adam_mixed_dev(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, int group, bool with_ctrl);
+
+// Brings the host mirrors up to date after asynchronous steps (synchronises the stream); no-op otherwise.
+int32_t collect_dev_state(nbo_optimizer *h);
 
 // ZeRO-1 fused with its collectives over peer / multicast mappings (transport: 0 local, 1 peer, 2 multicast)
 int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, const AdamHP &hp,

@@ -66,21 +66,23 @@ int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const Adam
     if (with_ctrl || hp.inv_scale != 1.0f) {
         int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<true>);
         adam_mixed_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp,
-                                                                with_ctrl ? h->d_ctrl : nullptr);
+                                                                with_ctrl ? h->d_ctrl : nullptr, nullptr);
     } else {
         int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<false>);
-        adam_mixed_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp, nullptr);
+        adam_mixed_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp, nullptr,
+                                                                 nullptr);
     }
     return launched(h);
 }
 
 template <bool kBf16, bool kCheckEach>
-static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, int finalize, const NormOut &out)
+static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, int finalize, const NormOut &out,
+                            const float *inv_scale_dev = nullptr)
 {
     uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;  // one loop iteration takes kNormBatch chunks
     int grid = grid_for(h, units, (const void *)norm_kernel<kBf16, kCheckEach>);
     norm_kernel<kBf16, kCheckEach><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
-                                                                  inv_scale, max_norm, finalize, out);
+                                                                  inv_scale, max_norm, finalize, out, inv_scale_dev);
 }
 
 int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize)
@@ -95,6 +97,37 @@ int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_nor
         if (each) launch_norm_one<false, true>(h, inv_scale, max_norm, finalize, out);
         else launch_norm_one<false, false>(h, inv_scale, max_norm, finalize, out);
     }
+    return launched(h);
+}
+
+// Asynchronous step: the unscale factor is read from device memory, so the per-element flag test is kept
+// (the host cannot know whether the factor exceeds 1).
+int32_t launch_norm_dev(nbo_optimizer *h, const float *inv_scale_dev, double max_norm)
+{
+    NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
+    launch_norm_one<true, true>(h, 1.0f, max_norm, 1, out, inv_scale_dev);
+    return launched(h);
+}
+
+int32_t launch_prepare(nbo_optimizer *h, int use_scaler)
+{
+    prepare_kernel<<<1, kMaxDevGroups, 0, h->stream>>>(h->d_state, h->d_hp, h->d_inv_scale, use_scaler);
+    return launched(h);
+}
+
+int32_t launch_commit(nbo_optimizer *h, bool checked, int use_scaler)
+{
+    commit_kernel<<<1, 32, 0, h->stream>>>(h->d_state, checked ? h->d_ctrl : nullptr, use_scaler);
+    return launched(h);
+}
+
+int32_t launch_adam_mixed_dev(nbo_optimizer *h, uint32_t cb, uint32_t nc, int group, bool with_ctrl)
+{
+    if (nc == 0) return NBO_OK;
+    AdamHP unused{};
+    int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<true>);
+    adam_mixed_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, unused,
+                                                            with_ctrl ? h->d_ctrl : nullptr, h->d_hp + group);
     return launched(h);
 }
 
@@ -344,9 +377,11 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
         if (grid < 1) grid = 1;
         NormOut out{s->partial_sum, s->partial_bad, &s->ticket, out_dev, &s->ctrl};
         if (bf16)
-            norm_kernel<true, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+            norm_kernel<true, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out,
+                                                                  nullptr);
         else
-            norm_kernel<false, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out);
+            norm_kernel<false, true><<<(int)grid, kBlock, 0, st>>>(&s->desc, s->chunks, nchunks, inv_scale, 0.0, 1, out,
+                                                                   nullptr);
         NBO_CUDA(nullptr, cudaGetLastError());
         return NBO_OK;
     }();

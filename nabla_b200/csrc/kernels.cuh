@@ -349,8 +349,10 @@ __device__ __forceinline__ void mixed_items(uint2 *p2, const uint2 *g2, float4 *
 template <bool kScaled>
 __global__ void __launch_bounds__(kBlock)
 adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
-                  uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl)
+                  uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl,
+                  const AdamHP *__restrict__ hp_dev)
 {
+    if (hp_dev != nullptr) hp = *hp_dev;  // asynchronous step: prepare_kernel wrote this group's scalars
     float clip = 1.0f;
     if (kScaled && ctrl != nullptr) {
         if (ctrl->skip)
@@ -489,8 +491,10 @@ constexpr int kNormBatch = 4;
 template <bool kBf16, bool kCheckEach>
 __global__ void __launch_bounds__(kBlock)
 norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
-            uint32_t nchunks, float inv_scale, double max_norm, int finalize, NormOut out)
+            uint32_t nchunks, float inv_scale, double max_norm, int finalize, NormOut out,
+            const float *__restrict__ inv_scale_dev)
 {
+    if (inv_scale_dev != nullptr) inv_scale = *inv_scale_dev;  // asynchronous step: the scale lives on the device
     double acc = 0.0, acc2 = 0.0;  // two chains: halves the DFMA dependency depth
     int bad = 0;
     const uint32_t stride = gridDim.x * kNormBatch;
@@ -614,6 +618,51 @@ __global__ void finalize_ranks_kernel(const double *__restrict__ gathered, int w
         bad |= gathered[2 * r + 1] != 0.0 ? 1 : 0;
     }
     write_ctrl(ctrl, tot, bad, max_norm);
+}
+
+// ---- device-resident step state (asynchronous / graph-captured step) ------------------------------
+// prepare_kernel: before a step, one thread per group turns the device-held configuration and step
+// counter into that group's AdamHP (for step_count + 1, as the host does for the synchronous step) and
+// publishes f32(1/scale).  commit_kernel: after the step, one thread applies the outcome to the state -
+// GradScaler::unscale_and_update's bookkeeping (core.rs:367-386) and the step counters, which do not
+// advance on a skipped step (trainer.rs:230-237).
+__global__ void prepare_kernel(const DevState *__restrict__ st, AdamHP *__restrict__ hp_out,
+                               float *__restrict__ inv_scale_out, int use_scaler)
+{
+    float inv_scale = use_scaler ? (float)(1.0 / st->scale) : 1.0f;
+    int g = threadIdx.x;
+    if (g < st->ngroups) {
+        const DevGroup &c = st->g[g];
+        hp_out[g] = adam_hparams_of(c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.kind == 0 /* AdamW */,
+                                    c.step_count + 1, inv_scale);
+    }
+    if (g == 0) *inv_scale_out = inv_scale;
+}
+
+__global__ void commit_kernel(DevState *st, const StepCtrl *__restrict__ ctrl, int use_scaler)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    bool bad = ctrl != nullptr && ctrl->nonfinite != 0;
+    if (bad) {
+        if (use_scaler) {
+            st->scale *= st->backoff_factor;
+            st->consecutive_ok = 0;
+        }
+    } else {
+        for (int g = 0; g < st->ngroups; ++g)
+            if (st->g[g].kind != 2 /* SGD */) st->g[g].step_count += 1;
+        if (use_scaler) {
+            st->consecutive_ok += 1;
+            if (st->consecutive_ok >= st->growth_interval) {
+                st->scale *= st->growth_factor;
+                st->consecutive_ok = 0;
+            }
+        }
+    }
+    st->last_applied = bad ? 0 : 1;
+    st->last_nonfinite = bad ? 1 : 0;
+    st->last_norm = (ctrl != nullptr && !bad) ? ctrl->norm : 0.0;
+    st->steps_enqueued += 1;
 }
 
 // ---- in-place fp32 gradient rewrite ---------------------------------------------

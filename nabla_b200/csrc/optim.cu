@@ -24,37 +24,11 @@ int32_t fail_cuda(nbo_optimizer *h, cudaError_t e, const char *what)
     return fail(h, code, m);
 }
 
-double powi(double a, int32_t b)
-{
-    uint32_t e = b < 0 ? (uint32_t)(-(int64_t)b) : (uint32_t)b;
-    double r = 1.0;
-    for (;;) {
-        if (e & 1u) r *= a;
-        e >>= 1;
-        if (e == 0) break;
-        a *= a;
-    }
-    return b < 0 ? 1.0 / r : r;
-}
+double powi(double a, int32_t b) { return powi_sqm(a, b); }
 
 AdamHP adam_hparams(const nbo_group_config &c, uint64_t step, float inv_scale)
 {
-    AdamHP h;
-    double bias_corr1 = 1.0 - powi(c.beta1, (int32_t)step);
-    double bias_corr2 = 1.0 - powi(c.beta2, (int32_t)step);
-    double step_size = c.lr / bias_corr1;
-    h.b1 = (float)c.beta1;
-    h.one_minus_b1 = (float)(1.0 - c.beta1);
-    h.b2 = (float)c.beta2;
-    h.one_minus_b2 = (float)(1.0 - c.beta2);
-    float wd_lr = (float)(c.weight_decay * c.lr);
-    h.eps = (float)c.eps;
-    h.ss = (float)step_size;
-    h.inv_bc2 = (float)(1.0 / bias_corr2);
-    h.decay = 1.0f - wd_lr;  // subtracted in f32 (alg.rs:135)
-    h.inv_scale = inv_scale;
-    h.decoupled = c.kind == NBO_ADAMW ? 1 : 0;
-    return h;
+    return adam_hparams_of(c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.kind == NBO_ADAMW, step, inv_scale);
 }
 
 SgdHP sgd_hparams(const nbo_group_config &c)
@@ -289,6 +263,30 @@ static int32_t read_ctrl(nbo_optimizer *h)
     return NBO_OK;
 }
 
+int32_t collect_dev_state(nbo_optimizer *h)
+{
+    if (!h->dev_newer) return NBO_OK;
+    NBO_CUDA(h, cudaMemcpyAsync(h->h_state, h->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, h->stream));
+    NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost, h->stream));
+    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    const DevState &st = *h->h_state;
+    h->scaler.scale = st.scale;
+    h->scaler.consecutive_ok = st.consecutive_ok;
+    for (size_t g = 0; g < h->groups.size() && g < (size_t)kMaxDevGroups; ++g)
+        h->groups[g].step_count = st.g[g].step_count;
+    h->dev_newer = false;
+    return NBO_OK;
+}
+
+// Every entry point that reads or changes host-side optimizer / scaler state starts with this.
+#define NBO_SYNC_STATE(h)                                          \
+    do {                                                           \
+        if ((h) && (h)->dev_newer) {                               \
+            int32_t rc__ = collect_dev_state((nbo_optimizer *)(h)); \
+            if (rc__ != NBO_OK) return rc__;                       \
+        }                                                          \
+    } while (0)
+
 struct DeviceGuard {
     int prev = -1;
     explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
@@ -339,6 +337,12 @@ int32_t nbo_create(int32_t device, void *stream, nbo_optimizer **out)
         NBO_CUDA(h, cudaMallocHost(&h->h_ctrl, sizeof(StepCtrl)));
         memset(h->h_ctrl, 0, sizeof(StepCtrl));
         NBO_CUDA(h, cudaEventCreateWithFlags(&h->upload_done, cudaEventDisableTiming));
+        NBO_CUDA(h, cudaMalloc(&h->d_state, sizeof(DevState)));
+        NBO_CUDA(h, cudaMemset(h->d_state, 0, sizeof(DevState)));
+        NBO_CUDA(h, cudaMallocHost(&h->h_state, sizeof(DevState)));
+        memset(h->h_state, 0, sizeof(DevState));
+        NBO_CUDA(h, cudaMalloc(&h->d_hp, kMaxDevGroups * sizeof(AdamHP)));
+        NBO_CUDA(h, cudaMalloc(&h->d_inv_scale, sizeof(float)));
         return NBO_OK;
     }();
     if (rc != NBO_OK) {
@@ -360,6 +364,8 @@ int32_t nbo_destroy(nbo_optimizer *h)
     cudaFree(h->d_partial_sum); cudaFree(h->d_partial_bad); cudaFree(h->d_ticket);
     cudaFree(h->d_local); cudaFree(h->d_ctrl);
     if (h->h_ctrl) cudaFreeHost(h->h_ctrl);
+    cudaFree(h->d_state); cudaFree(h->d_hp); cudaFree(h->d_inv_scale);
+    if (h->h_state) cudaFreeHost(h->h_state);
     if (h->upload_done) cudaEventDestroy(h->upload_done);
     for (cudaEvent_t e : h->prof_ev)
         if (e) cudaEventDestroy(e);
@@ -427,6 +433,7 @@ int32_t nbo_set_tensors(nbo_optimizer *h, uint64_t n, const uint64_t *numel, con
 
 int32_t nbo_step(nbo_optimizer *h, uint64_t n, void *const *params, const void *const *grads)
 {
+    NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     if (h->configured && h->precision != NBO_F32)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_step needs an fp32 handle; use nbo_step_mixed");
@@ -452,6 +459,7 @@ int32_t nbo_step(nbo_optimizer *h, uint64_t n, void *const *params, const void *
 
 int32_t nbo_reset(nbo_optimizer *h)
 {
+    NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     DeviceGuard guard(h->device);
     for (Group &g : h->groups) g.step_count = 0;
@@ -467,6 +475,7 @@ int32_t nbo_reset(nbo_optimizer *h)
 
 int32_t nbo_set_lr(nbo_optimizer *h, double lr)
 {
+    NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     if (h->groups.empty()) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: no group");
     if (h->groups.size() == 1) {
@@ -494,6 +503,7 @@ static int32_t check_group(const nbo_optimizer *h, int32_t gid)
 
 int32_t nbo_get_lr(const nbo_optimizer *h, int32_t gid, double *lr)
 {
+    NBO_SYNC_STATE(h);
     int32_t rc = check_group(h, gid);
     if (rc != NBO_OK) return rc;
     if (lr) *lr = h->groups[gid].cfg.lr;
@@ -502,6 +512,7 @@ int32_t nbo_get_lr(const nbo_optimizer *h, int32_t gid, double *lr)
 
 int32_t nbo_step_count(const nbo_optimizer *h, int32_t gid, uint64_t *count)
 {
+    NBO_SYNC_STATE(h);
     int32_t rc = check_group(h, gid);
     if (rc != NBO_OK) return rc;
     if (count) *count = h->groups[gid].step_count;
@@ -510,6 +521,7 @@ int32_t nbo_step_count(const nbo_optimizer *h, int32_t gid, uint64_t *count)
 
 int32_t nbo_set_step_count(nbo_optimizer *h, int32_t gid, uint64_t count)
 {
+    NBO_SYNC_STATE(h);
     int32_t rc = check_group(h, gid);
     if (rc != NBO_OK) return rc;
     h->groups[gid].step_count = count;
@@ -518,6 +530,7 @@ int32_t nbo_set_step_count(nbo_optimizer *h, int32_t gid, uint64_t count)
 
 int32_t nbo_get_group(const nbo_optimizer *h, int32_t gid, nbo_group_config *cfg)
 {
+    NBO_SYNC_STATE(h);
     int32_t rc = check_group(h, gid);
     if (rc != NBO_OK) return rc;
     if (cfg) *cfg = h->groups[gid].cfg;
@@ -526,6 +539,7 @@ int32_t nbo_get_group(const nbo_optimizer *h, int32_t gid, nbo_group_config *cfg
 
 int32_t nbo_set_group(nbo_optimizer *h, int32_t gid, const nbo_group_config *cfg)
 {
+    NBO_SYNC_STATE(h);
     int32_t rc = check_group(h, gid);
     if (rc != NBO_OK) return rc;
     if (!cfg) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null config");
@@ -579,6 +593,7 @@ int32_t nbo_state_import(nbo_optimizer *h, uint64_t tensor, int32_t which, const
 
 int32_t nbo_scaler_get(const nbo_optimizer *h, nbo_scaler_state *out)
 {
+    NBO_SYNC_STATE(h);
     if (!h || !out) return fail(const_cast<nbo_optimizer *>(h), NBO_ERR_INVALID, "nabla-optim-b200: null argument");
     *out = h->scaler;
     return NBO_OK;
@@ -586,6 +601,7 @@ int32_t nbo_scaler_get(const nbo_optimizer *h, nbo_scaler_state *out)
 
 int32_t nbo_scaler_set(nbo_optimizer *h, const nbo_scaler_state *in)
 {
+    NBO_SYNC_STATE(h);
     if (!h || !in) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null argument");
     h->scaler = *in;
     return NBO_OK;
@@ -616,6 +632,7 @@ int32_t nbo_accumulate_grads(nbo_optimizer *h, uint64_t n, void *const *accum, c
 
 int32_t nbo_unscale_and_update(nbo_optimizer *h, uint64_t n, void *const *grads, int32_t *ok)
 {
+    NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     if (n && !grads) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null pointer list");
     if (h->configured && h->precision != NBO_F32)
@@ -702,6 +719,7 @@ int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
                        const void *const *grads_bf16, int32_t use_scaler, double max_norm,
                        nbo_step_result *result)
 {
+    NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     if (h->configured && h->precision != NBO_MIXED_BF16)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_step_mixed needs a mixed-precision handle");
@@ -730,6 +748,69 @@ int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
         NBO_CUDA(h, cudaStreamSynchronize(h->stream));
     }
     commit_step(h, checked, use_scaler != 0, result);
+    return NBO_OK;
+}
+
+int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
+                             const void *const *grads_bf16, int32_t use_scaler, double max_norm)
+{
+    if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
+    if (!h->configured || h->precision != NBO_MIXED_BF16 || h->zero1)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_step_mixed_async needs an unsharded mixed-precision handle");
+    if (h->groups.size() > (size_t)kMaxDevGroups)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: the asynchronous step supports at most 32 groups");
+    if (n && (!params_bf16 || !grads_bf16))
+        return fail(h, NBO_ERR_INVALID, "nabla-train: params/grads length mismatch (null list)");
+    DeviceGuard guard(h->device);
+    int32_t rc = bind_list(h, n, params_bf16, grads_bf16, 2, "step");
+    if (rc != NBO_OK) return rc;
+    if (!h->dev_newer) {  // the host holds the current state: send it down (stream-ordered)
+        DevState &st = *h->h_state;
+        st.scale = h->scaler.scale; st.growth_factor = h->scaler.growth_factor;
+        st.backoff_factor = h->scaler.backoff_factor; st.growth_interval = h->scaler.growth_interval;
+        st.consecutive_ok = h->scaler.consecutive_ok; st.ngroups = (int32_t)h->groups.size();
+        for (size_t g = 0; g < h->groups.size(); ++g) {
+            const nbo_group_config &c = h->groups[g].cfg;
+            st.g[g] = DevGroup{c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.kind, 0, h->groups[g].step_count};
+        }
+        NBO_CUDA(h, cudaMemcpyAsync(h->d_state, h->h_state, sizeof(DevState), cudaMemcpyHostToDevice, h->stream));
+    }
+    bool checked = use_scaler || max_norm > 0.0;
+    rc = launch_prepare(h, use_scaler);
+    if (rc != NBO_OK) return rc;
+    if (checked) {
+        rc = launch_norm_dev(h, h->d_inv_scale, max_norm);
+        if (rc != NBO_OK) return rc;
+    }
+    for (size_t g = 0; g < h->groups.size(); ++g) {
+        const Group &gr = h->groups[g];
+        rc = launch_adam_mixed_dev(h, gr.chunk_begin, gr.chunk_end - gr.chunk_begin, (int)g, checked);
+        if (rc != NBO_OK) return rc;
+    }
+    rc = launch_commit(h, checked, use_scaler);
+    if (rc != NBO_OK) return rc;
+    h->dev_newer = true;
+    h->last_async_checked = checked;
+    return NBO_OK;
+}
+
+int32_t nbo_step_mixed_collect(nbo_optimizer *h, nbo_step_result *result, uint64_t *steps_enqueued)
+{
+    if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
+    if (!h->dev_newer && h->h_state->ngroups == 0)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: no asynchronous step has been enqueued");
+    DeviceGuard guard(h->device);
+    int32_t rc = collect_dev_state(h);
+    if (rc != NBO_OK) return rc;
+    const DevState &st = *h->h_state;
+    if (result) {
+        result->applied = st.last_applied;
+        result->nonfinite = st.last_nonfinite;
+        result->grad_norm = st.last_norm;
+        result->loss_scale = st.scale;
+        result->step_count = st.ngroups > 0 ? st.g[0].step_count : 0;
+    }
+    if (steps_enqueued) *steps_enqueued = st.steps_enqueued;
     return NBO_OK;
 }
 

@@ -55,6 +55,71 @@ struct SgdHP {
     int32_t use_mu, use_wd;
 };
 
+// Optimizer / scaler state kept on the device for the asynchronous step, so that a whole step (and a
+// CUDA graph of it) runs without the host: the step counters and the loss scale advance on the device.
+constexpr int kMaxDevGroups = 32;
+struct DevGroup {
+    double lr, beta1, beta2, eps, weight_decay;
+    int32_t kind;  // nbo_kind
+    int32_t pad;
+    uint64_t step_count;
+};
+struct DevState {
+    double scale, growth_factor, backoff_factor;
+    uint64_t growth_interval, consecutive_ok;
+    int32_t ngroups;
+    int32_t last_applied;    // outcome of the most recent asynchronous step
+    int32_t last_nonfinite;
+    int32_t pad;
+    double last_norm;
+    uint64_t steps_enqueued;
+    DevGroup g[kMaxDevGroups];
+};
+
+#ifdef __CUDACC__
+#define NBO_HD __host__ __device__
+#else
+#define NBO_HD
+#endif
+
+// f64::powi as the reference's toolchain computes it: square-and-multiply, low bit first.
+NBO_HD inline double powi_sqm(double a, int32_t b)
+{
+    uint32_t e = b < 0 ? (uint32_t)(-(int64_t)b) : (uint32_t)b;
+    double r = 1.0;
+    for (;;) {
+        if (e & 1u) r *= a;
+        e >>= 1;
+        if (e == 0) break;
+        a *= a;
+    }
+    return b < 0 ? 1.0 / r : r;
+}
+
+// Host scalars of one Adam/AdamW step narrowed to f32 once each (alg.rs:120-135).  The same code runs on
+// the host (synchronous step) and in prepare_kernel (asynchronous step); IEEE double arithmetic gives
+// the same bits in both places.
+NBO_HD inline AdamHP adam_hparams_of(double lr, double beta1, double beta2, double eps, double weight_decay,
+                                     bool decoupled, uint64_t step, float inv_scale)
+{
+    AdamHP h;
+    double bias_corr1 = 1.0 - powi_sqm(beta1, (int32_t)step);
+    double bias_corr2 = 1.0 - powi_sqm(beta2, (int32_t)step);
+    double step_size = lr / bias_corr1;
+    h.b1 = (float)beta1;
+    h.one_minus_b1 = (float)(1.0 - beta1);
+    h.b2 = (float)beta2;
+    h.one_minus_b2 = (float)(1.0 - beta2);
+    float wd_lr = (float)(weight_decay * lr);
+    h.eps = (float)eps;
+    h.ss = (float)step_size;
+    h.inv_bc2 = (float)(1.0 / bias_corr2);
+    h.decay = 1.0f - wd_lr;  // subtracted in f32 (alg.rs:135)
+    h.inv_scale = inv_scale;
+    h.decoupled = decoupled ? 1 : 0;
+    return h;
+}
+
 // Where the other ranks' copies of the two flat buckets are mapped in this
 // process (symmetric memory), as byte offsets from this rank's own bucket so
 // that "address of element i on rank r" = local address + delta.

@@ -670,6 +670,19 @@ class MixedAdamW:
                                                  1 if use_scaler else 0, float(max_norm), C.byref(res)))
         return StepOutcome.from_c(res)
 
+    def step_async(self, params_arr, grads_arr, *, use_scaler=True, max_norm=0.0) -> None:
+        """Enqueues one step and returns without waiting; the step counter, bias corrections and loss-scale
+        bookkeeping advance on the device.  Every launch has constant arguments, so the call can be captured
+        into a CUDA graph and replayed.  `collect()` (or any state accessor) hands the state back."""
+        self._h.check(self._h.lib.nbo_step_mixed_async(self._h.h, len(self._numel), params_arr, grads_arr,
+                                                       1 if use_scaler else 0, float(max_norm)))
+
+    def collect(self):
+        """(outcome of the most recent asynchronous step, asynchronous steps completed on the device)."""
+        res, k = L.StepResult(), C.c_uint64()
+        self._h.check(self._h.lib.nbo_step_mixed_collect(self._h.h, C.byref(res), C.byref(k)))
+        return StepOutcome.from_c(res), k.value
+
     def set_lr(self, lr: float) -> None:
         self._h.check(self._h.lib.nbo_set_lr(self._h.h, float(lr)))
 
