@@ -316,6 +316,15 @@ NBO_API int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *num
                                const int32_t *group_ids, int32_t rank, int32_t world,
                                const uint8_t unique_id[128]);
 
+/* Host-side time limit (seconds, default 600) for joining the communicator and
+ * for the completion of each sharded step.  When it runs out - a rank never
+ * arrived, or stopped taking part - the communicator is aborted, the call
+ * returns NBO_ERR_TIMEOUT, the CUDA context stays usable and later sharded
+ * steps on this handle return NBO_ERR_STATE.  May be called before or after
+ * nbo_zero1_init.  The reference's counterpart is the Err("send failed") of
+ * its channel pair (nabla-train/src/dist.rs:37-40). */
+NBO_API int32_t nbo_zero1_set_timeout(nbo_optimizer *h, double seconds);
+
 /* Seeds this rank's fp32 master shard from the flat bf16 param bucket. */
 NBO_API int32_t nbo_zero1_init_master(nbo_optimizer *h, const void *params_flat_bf16);
 

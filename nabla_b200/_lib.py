@@ -91,6 +91,7 @@ SIGNATURES = {
     "nbo_zero1_unique_id": (C.c_int32, [C.c_void_p]),
     "nbo_zero1_geometry": (C.c_int32, [C.c_uint64, C.c_int32, _U64P, _U64P]),
     "nbo_zero1_init": (C.c_int32, [_H, C.c_uint64, _U64P, _I32P, C.c_int32, C.c_int32, C.c_void_p]),
+    "nbo_zero1_set_timeout": (C.c_int32, [_H, C.c_double]),
     "nbo_zero1_init_master": (C.c_int32, [_H, C.c_void_p]),
     "nbo_zero1_step": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_double,
                                    C.POINTER(StepResult)]),

@@ -91,6 +91,7 @@ struct nbo_optimizer {
     uint64_t launches = 0;
 
     nbo::Zero1 *zero1 = nullptr;
+    double zero1_timeout_s = 600.0;
 };
 
 namespace nbo {

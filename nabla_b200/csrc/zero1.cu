@@ -11,6 +11,9 @@
 #include <nccl.h>
 #include <string.h>
 
+#include <chrono>
+#include <thread>
+
 #include "internal.h"
 
 namespace nbo {
@@ -18,7 +21,8 @@ namespace nbo {
 struct NcclApi {
     void *lib = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
-    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
@@ -50,7 +54,8 @@ static NcclApi *nccl_api()
         if (!api.field) { api.why = std::string("NCCL symbol missing: ") + name; } \
     } while (0)
     NBO_SYM(GetUniqueId, "ncclGetUniqueId");
-    NBO_SYM(CommInitRank, "ncclCommInitRank");
+    NBO_SYM(CommInitRankConfig, "ncclCommInitRankConfig");
+    NBO_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     NBO_SYM(CommDestroy, "ncclCommDestroy");
     NBO_SYM(CommAbort, "ncclCommAbort");
     NBO_SYM(ReduceScatter, "ncclReduceScatter");
@@ -64,7 +69,9 @@ static NcclApi *nccl_api()
 struct Zero1 {
     int rank = 0, world = 1;
     uint64_t total = 0, shard = 0, padded = 0, begin = 0, end = 0;
-    ncclComm_t comm = nullptr;
+    ncclComm_t comm = nullptr;  // non-blocking communicator: every call is followed by a bounded wait
+    double timeout_s = 600.0;   // host-side limit for joining the communicator and for each step's completion
+    bool broken = false;        // the communicator was aborted after a timeout or an error
     double *d_gathered = nullptr;  // {sumsq, nonfinite} of every rank, rank order
     // fused path: symmetric-memory buckets
     bool attached = false;
@@ -82,17 +89,73 @@ static int32_t fail_nccl(nbo_optimizer *h, ncclResult_t r, const char *what)
     return fail(h, NBO_ERR_NCCL, m);
 }
 
-#define NBO_NCCL(h, call)                                  \
-    do {                                                   \
-        ncclResult_t r__ = (call);                         \
-        if (r__ != ncclSuccess) return fail_nccl((h), r__, #call); \
+using Clock = std::chrono::steady_clock;
+
+static void abort_comm(Zero1 *z)
+{
+    if (z->comm) nccl_api()->CommAbort(z->comm);  // also ends an NCCL kernel that waits for a rank that is gone
+    z->comm = nullptr;
+    z->broken = true;
+}
+
+// Failure detection lives on the host: a non-blocking NCCL call is followed until the communicator reports
+// success, an error, or the time limit; on the limit the communicator is aborted and the caller gets
+// NBO_ERR_TIMEOUT with the CUDA context intact.  No device code waits on another rank.
+static int32_t nccl_wait(nbo_optimizer *h, Zero1 *z, ncclResult_t r, const char *what)
+{
+    NcclApi *a = nccl_api();
+    const auto deadline = Clock::now() + std::chrono::duration<double>(z->timeout_s);
+    while (r == ncclSuccess || r == ncclInProgress) {
+        ncclResult_t st = ncclSuccess;
+        ncclResult_t q = a->CommGetAsyncError(z->comm, &st);
+        if (q != ncclSuccess) { r = q; break; }
+        if (st == ncclSuccess) return NBO_OK;
+        if (st != ncclInProgress) { r = st; break; }
+        if (Clock::now() > deadline) {
+            abort_comm(z);
+            return fail(h, NBO_ERR_TIMEOUT, std::string("nabla-optim-b200: timed out after ") +
+                                                std::to_string(z->timeout_s) + " s in " + what +
+                                                " (a rank did not arrive); communicator aborted");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    abort_comm(z);
+    return fail_nccl(h, r, what);
+}
+
+// Bounded replacement for cudaStreamSynchronize on a stream that carries collectives.
+static int32_t stream_wait(nbo_optimizer *h, Zero1 *z, const char *what)
+{
+    const auto deadline = Clock::now() + std::chrono::duration<double>(z->timeout_s);
+    for (;;) {
+        cudaError_t e = cudaStreamQuery(h->stream);
+        if (e == cudaSuccess) return NBO_OK;
+        if (e != cudaErrorNotReady) return fail_cuda(h, e, what);
+        if (z->world > 1 && Clock::now() > deadline) {
+            abort_comm(z);                       // lets the stuck collective return
+            cudaStreamSynchronize(h->stream);    // what follows it on the stream touches local memory only
+            return fail(h, NBO_ERR_TIMEOUT, std::string("nabla-optim-b200: timed out after ") +
+                                                std::to_string(z->timeout_s) + " s waiting for " + what +
+                                                " (a rank stopped taking part); communicator aborted");
+        }
+        std::this_thread::yield();
+    }
+}
+
+#define NBO_NCCL(h, call)                                   \
+    do {                                                    \
+        int32_t rc__ = nccl_wait((h), z, (call), #call);    \
+        if (rc__ != NBO_OK) return rc__;                    \
     } while (0)
 
 void zero1_destroy(nbo_optimizer *h)
 {
     if (!h->zero1) return;
     Zero1 *z = h->zero1;
-    if (z->comm) nccl_api()->CommDestroy(z->comm);
+    if (z->comm) {
+        cudaStreamSynchronize(h->stream);
+        nccl_api()->CommDestroy(z->comm);
+    }
     cudaFree(z->d_gathered);
     cudaFree(z->d_barrier);
     delete z;
@@ -162,6 +225,7 @@ int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *numel, cons
 
     Zero1 *z = new Zero1();
     z->rank = rank; z->world = world;
+    z->timeout_s = h->zero1_timeout_s;
     uint64_t total = 0;
     for (uint64_t t = 0; t < n; ++t) total += numel[t];
     z->total = total;
@@ -200,8 +264,19 @@ int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *numel, cons
         NBO_CUDA(h, cudaMalloc(&z->d_gathered, 2 * sizeof(double) * world));
         ncclUniqueId id;
         memcpy(&id, unique_id, 128);
-        NBO_NCCL(h, a->CommInitRank(&z->comm, world, id, rank));
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.blocking = 0;  // so that a rank that never arrives ends in a timeout, not in a hang
+        NBO_NCCL(h, a->CommInitRankConfig(&z->comm, world, id, rank, &config));
     }
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_set_timeout(nbo_optimizer *h, double seconds)
+{
+    if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
+    if (!(seconds > 0.0)) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: the timeout must be positive");
+    h->zero1_timeout_s = seconds;
+    if (h->zero1) h->zero1->timeout_s = seconds;
     return NBO_OK;
 }
 
@@ -234,6 +309,7 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
     if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
     if (!params_flat || !grads_flat) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
     Zero1 *z = h->zero1;
+    if (z->broken) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
     cudaError_t ce = cudaSetDevice(h->device);
     if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
     NcclApi *a = z->world > 1 ? nccl_api() : nullptr;
@@ -273,7 +349,8 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
         NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
                                     h->stream));
     }
-    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    rc = stream_wait(h, z, "the sharded step");
+    if (rc != NBO_OK) return rc;
     commit_step(h, checked, use_scaler != 0, result);
     return NBO_OK;
 }
@@ -329,6 +406,7 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
     Zero1 *z = h->zero1;
     if (!z->attached)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_zero1_step_fused before nbo_zero1_attach_symmetric");
+    if (z->broken) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
     cudaError_t ce = cudaSetDevice(h->device);
     if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
     NcclApi *a = nccl_api();
@@ -339,6 +417,11 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
 
     // every rank's gradients are final, and nobody still reads the old params, before any peer access
     NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, h->stream));
+    // The kernels below read and write the other ranks' memory.  They are enqueued only once the barrier is
+    // known to have completed, so a rank that has gone away ends this call with a timeout before anything
+    // touches its memory.
+    rc = stream_wait(h, z, "the barrier before the fused step");
+    if (rc != NBO_OK) return rc;
 
     bool checked = use_scaler || max_norm > 0.0;
     float inv_scale = use_scaler ? (float)(1.0 / h->scaler.scale) : 1.0f;
@@ -368,7 +451,8 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
     if (checked)
         NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
                                     h->stream));
-    NBO_CUDA(h, cudaStreamSynchronize(h->stream));
+    rc = stream_wait(h, z, "the fused sharded step");
+    if (rc != NBO_OK) return rc;
     commit_step(h, checked, use_scaler != 0, result);
     return NBO_OK;
 }

@@ -65,7 +65,7 @@ class Zero1AdamW:
 
     def __init__(self, names, shapes, groups: Sequence[ParamGroupConfig],
                  default_group: Optional[ParamGroupConfig], rank: int, world: int,
-                 unique_id: Optional[bytes] = None, *, device=None, stream=None):
+                 unique_id: Optional[bytes] = None, *, device=None, stream=None, timeout_s: Optional[float] = None):
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
         self._configs, self._gid_of = kept, gid_of
@@ -79,6 +79,8 @@ class Zero1AdamW:
         arr = (C.c_uint64 * n)(*self._numel)
         gids = (C.c_int32 * n)(*gid_of)
         uid = (C.c_uint8 * 128)(*unique_id) if unique_id is not None else None
+        if timeout_s is not None:
+            self._h.check(self._h.lib.nbo_zero1_set_timeout(self._h.h, float(timeout_s)))
         self._h.check(self._h.lib.nbo_zero1_init(self._h.h, n, arr, gids, rank, world, uid))
 
     @classmethod
@@ -86,6 +88,10 @@ class Zero1AdamW:
         names = [f"p{i}" for i in range(len(shapes))]
         return cls(names, shapes, [], ParamGroupConfig.adamw("all", ParamSelector.All(), lr, weight_decay),
                    rank, world, unique_id, **kw)
+
+    def set_timeout(self, seconds: float) -> None:
+        """Host-side limit for each sharded step; on expiry the step raises with status NBO_ERR_TIMEOUT."""
+        self._h.check(self._h.lib.nbo_zero1_set_timeout(self._h.h, float(seconds)))
 
     def shard_range(self) -> Tuple[int, int, int]:
         b, e, p = C.c_uint64(), C.c_uint64(), C.c_uint64()

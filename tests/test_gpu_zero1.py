@@ -85,3 +85,32 @@ def test_multi_gpu_matches_single_gpu(world, mode):
     if "ZERO1_WORKER_SKIP" in r.stdout:
         pytest.skip(r.stdout.strip().splitlines()[-1])
     assert "ZERO1_WORKER_OK" in r.stdout
+
+
+def test_rank_that_never_arrives_times_out(nb):
+    """Communicator set-up with a peer that never calls in: NBO_ERR_TIMEOUT after the limit, context intact."""
+    import ctypes as C
+    import time
+    L = nb._lib
+    uid = (C.c_uint8 * 128)()
+    L.check(None, L.load().nbo_zero1_unique_id(uid))
+    t0 = time.time()
+    with pytest.raises(L.NablaOptimError) as ei:
+        nb.Zero1AdamW.adamw(1e-3, 0.0, [(1000,)], 0, 2, bytes(uid), timeout_s=2.0)
+    assert ei.value.code == L.NBO_ERR_TIMEOUT and "did not arrive" in ei.value.message
+    assert 1.5 < time.time() - t0 < 30.0
+    p = torch.ones(100, device="cuda")
+    nb.Sgd(0.1, [(100,)]).step([p], [torch.ones(100, device="cuda")])
+    assert abs(float(p[0]) - 0.9) < 1e-6
+
+
+@pytest.mark.parametrize("mode", ["nccl", "peer"])
+def test_rank_leaving_between_steps_ends_in_a_timeout(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29580 + (mode == "peer")),
+           os.path.join(ROOT, "tests", "zero1_leave_worker.py"), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert "ZERO1_LEAVE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
