@@ -28,7 +28,7 @@ import numpy as np
 import torch
 
 from . import _lib as L
-from .optim import (Adam, AdamW, GradScaler, GroupOptimizer, LrSchedule, MixedAdamW, Optimizer, Sgd)
+from .optim import GroupOptimizer, LrSchedule, MixedAdamW
 
 NBLA_MAGIC = b"NBLA"
 META_FILE, PARAMS_FILE, OPTIM_FILE = "meta.txt", "params.nbla", "optim.nbla"

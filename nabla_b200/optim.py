@@ -19,7 +19,7 @@ returns ``Err(String)`` this raises ValueError with the same text.
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
 import torch

@@ -16,7 +16,6 @@ Every tensor op is a kernel of libnabla_optim_b200 over the device table; nothin
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional, Sequence, Tuple
 
 import torch

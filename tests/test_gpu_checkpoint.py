@@ -1,6 +1,4 @@
 """GPU: checkpoint / resume in the reference's directory format: a resumed optimizer continues bit for bit."""
-import os
-
 import numpy as np
 import pytest
 import torch

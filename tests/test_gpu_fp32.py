@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import REL_TOL, assert_close_rel, bits, dev, exact_fraction, host, misaligned
+from util import assert_close_rel, bits, dev, exact_fraction, host, misaligned
 
 pytestmark = pytest.mark.gpu
 

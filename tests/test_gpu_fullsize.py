@@ -1,4 +1,4 @@
-"""GPU: the BASELINE configurations at their full sizes, checked through properties that do not need a CPU run
+"""GPU: the benchmark configurations at their full sizes, checked through properties that do not need a CPU run
 of the whole thing: independence of the tensor partition (elementwise work must not care how a buffer is cut
 into tensors), cast exactness over every element, all-or-nothing skip, and the oracle on seeded slices."""
 import math

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import assert_close_rel, bf16_bits, bf16_dev, bits, exact_fraction, host
+from util import assert_close_rel, bf16_bits, bf16_dev, bits, exact_fraction
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_vectors.npz"))

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import assert_close_rel, bits, dev
+from util import assert_close_rel, dev
 
 pytestmark = pytest.mark.gpu
 
