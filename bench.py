@@ -462,6 +462,18 @@ def run_ours(args, wl_name, wl):
         "wall_ms_per_step": wall * 1e3 / args.steps,
     }
     line["config"].update(extra)
+    if wl["kind"] == "zero1" and world > 1:
+        # bytes that must cross NVLink per GPU and direction for one step, against the measured 770 GB/s peer copy
+        bucket = 2.0 * padded
+        path = extra.get("zero1_path", "")
+        tr = "mcast" if (path == "fused-mcast" or (path == "fused-auto" and world >= 4)) else (
+            "peer" if path.startswith("fused") else "nccl")
+        per_dir = bucket * (1.0 + 1.0 / world) if tr == "mcast" else 2.0 * bucket * (world - 1) / world
+        step_s = dev_s / args.steps
+        line["nvlink"] = {"transport": tr, "bytes_per_gpu_per_direction": per_dir, "peak": 770.0, "unit": "GB/s",
+                          "achieved": per_dir / step_s / 1e9, "frac": per_dir / step_s / 1e9 / 770.0,
+                          "target_ms": per_dir / 770e9 * 1e3,
+                          "note": "the sharded step is NVLink-bound for N >= 2; roofline.frac is the local HBM share only"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         mixed = wl["kind"] != "f32"
         sample = min(calibrated_cpu_sample(12.0, mixed), total)
