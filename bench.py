@@ -396,6 +396,29 @@ def run_ours(args, wl_name, wl):
     norm_ms = max_over_ranks(norm_ms / args.steps)
     value = total * args.steps / dev_s
 
+    # context for the roofline fraction: the same copy the peak was measured with (torch copy_, 2 x 2 GiB),
+    # but run back to back for as long as the timed region lasted, i.e. under the same power cap
+    copy_sustained = None
+    if world == 1 and not args.no_copy_probe:
+        try:
+            src = torch.empty(1 << 30, dtype=torch.bfloat16, device=dev).normal_()
+            dst = torch.empty_like(src)
+            reps = max(8, int(max(dev_s, 0.2) / 0.00066))
+            for _ in range(3):
+                dst.copy_(src)
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(reps // 2):
+                dst.copy_(src)
+            c0.record()
+            for _ in range(reps - reps // 2):
+                dst.copy_(src)
+            c1.record()
+            torch.cuda.synchronize()
+            copy_sustained = (reps - reps // 2) * 2 * src.numel() * 2 / (c0.elapsed_time(c1) * 1e-3) / 1e9
+            del src, dst
+        except RuntimeError:
+            copy_sustained = None
+
     # SGD has step-independent launch arguments, so a run of steps can be captured once and replayed
     # (Adam/AdamW bias corrections change every step; their graph-capturable form is the asynchronous mixed step)
     if wl["kind"] == "f32" and wl.get("opt") in ("sgd", "sgdm"):
@@ -451,6 +474,7 @@ def run_ours(args, wl_name, wl):
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": upd_ms, "traffic": traffic,
+                     "copy_sustained_gbs": copy_sustained,
                      "traffic_note": "ncu dram bytes of a small case of this kernel, scaled by elements per launch"},
         "kernel_ms": {"update": upd_ms, "norm_nonfinite": norm_ms},
         "step_hbm_gbs_per_gpu": step_bytes / (dev_s / args.steps) / 1e9,
@@ -496,6 +520,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama8b_zero1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-copy-probe", action="store_true")
     ap.add_argument("--zero1-path", choices=["auto", "peer", "mcast", "nccl"], default="auto",
                     help="N > 1: collectives fused into the kernels (auto/peer/mcast) or issued through NCCL")
     args = ap.parse_args()
