@@ -346,11 +346,10 @@ __device__ __forceinline__ void mixed_items(uint2 *p2, const uint2 *g2, float4 *
 }
 
 // kScaled = false is the plain step (no loss scale, no clipping, no decision record).
-#ifndef NBO_MIXED_MIN_CTAS
-#define NBO_MIXED_MIN_CTAS 2  // resident CTAs per SM the register budget is sized for
-#endif
+// 85 registers -> 2 resident CTAs per SM.  Forcing 3 (80 registers) was measured slower on the 8 G-element
+// case (40.8 vs 36.2 ms): more loads in flight than the memory system absorbs.
 template <bool kScaled>
-__global__ void __launch_bounds__(kBlock, NBO_MIXED_MIN_CTAS)
+__global__ void __launch_bounds__(kBlock)
 adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
                   uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl,
                   const AdamHP *__restrict__ hp_dev)
