@@ -346,8 +346,9 @@ __device__ __forceinline__ void mixed_items(uint2 *p2, const uint2 *g2, float4 *
 }
 
 // kScaled = false is the plain step (no loss scale, no clipping, no decision record).
-// 85 registers -> 2 resident CTAs per SM.  Forcing 3 (80 registers) was measured slower on the 8 G-element
-// case (40.8 vs 36.2 ms): more loads in flight than the memory system absorbs.
+// 2 resident CTAs per SM (register-limited).  Forcing 3 (80 registers) was measured slower on the 8 G-element
+// case (40.8 vs 36.2 ms): more loads in flight than the memory system absorbs; a tighter register budget at
+// the same 2 CTAs made no difference.
 template <bool kScaled>
 __global__ void __launch_bounds__(kBlock)
 adam_mixed_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
