@@ -14,8 +14,8 @@
 //           and multimem.st (the switch replicates the store).  Per GPU and
 //           direction: bucket x (1 + 1/N) bytes.  Best for N >= 4.
 //
-// Only plain loads/stores and multimem are used on remote memory: no TMA, no
-// cluster multicast.  The kernels contain no cross-GPU waits of their own; the
+// Only plain loads/stores and multimem instructions touch remote memory; no
+// tensor-map or bulk-copy engine is involved.  The kernels contain no cross-GPU waits of their own; the
 // host orders them with stream-ordered NCCL barriers (see zero1.cu), so nothing
 // here can spin.
 //
