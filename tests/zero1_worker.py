@@ -31,8 +31,13 @@ def main():
     sizes = [5, 4096, 3, 70001, 1, 8192, 2, 100000]
     total = sum(sizes)
     uid = nb.exchange_unique_id(rank, world)
-    z = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], rank, world, uid)
-    ref = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], 0, 1)      # single-GPU twin, full bucket
+    # two parameter groups (no weight decay on the "norm" tensors): group ranges must survive sharding
+    names = ["w0", "w1", "norm2", "w3", "norm4", "w5", "norm6", "w7"]
+    shapes = [(n,) for n in sizes]
+    nd = [nb.ParamGroupConfig.adamw("no_decay", nb.ParamSelector.Any([nb.ParamMatch.Prefix("norm")]), 3e-4, 0.0)]
+    dec = nb.ParamGroupConfig.adamw("decay", nb.ParamSelector.All(), 3e-4, 0.1)
+    z = nb.Zero1AdamW(names, shapes, nd, dec, rank, world, uid)
+    ref = nb.Zero1AdamW(names, shapes, nd, dec, 0, 1)                      # single-GPU twin, full bucket
     padded = z.padded
     assert ref.padded <= padded
     g0 = torch.Generator(device="cuda").manual_seed(1234)
