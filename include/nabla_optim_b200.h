@@ -55,7 +55,9 @@ typedef enum { NBO_ADAMW = 0, NBO_ADAM = 1, NBO_SGD = 2 } nbo_kind;
 /* Element type of the caller's params/grads. */
 typedef enum {
     NBO_F32 = 0,       /* params, grads and state all fp32 (Optimizer<f32, Cuda>)     */
-    NBO_MIXED_BF16 = 1 /* bf16 params+grads, fp32 master/m/v held by the handle       */
+    NBO_MIXED_BF16 = 1, /* bf16 params+grads, fp32 master/m/v held by the handle      */
+    NBO_MIXED_BF16_F32GRAD = 2 /* bf16 params, fp32 grads (e.g. accumulated over
+                                  micro-batches in fp32), fp32 master/m/v                 */
 } nbo_precision;
 
 /* One parameter group = ParamGroupConfig (nabla-train/src/optim/groups.rs:40-51).

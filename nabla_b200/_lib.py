@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libnabla_optim_b200.so")
 NBO_OK = 0
 NBO_ERR_INVALID, NBO_ERR_CUDA, NBO_ERR_NCCL, NBO_ERR_TIMEOUT, NBO_ERR_STATE, NBO_ERR_NOMEM = 1, 2, 3, 4, 5, 6
 NBO_ADAMW, NBO_ADAM, NBO_SGD = 0, 1, 2
-NBO_F32, NBO_MIXED_BF16 = 0, 1
+NBO_F32, NBO_MIXED_BF16, NBO_MIXED_BF16_F32GRAD = 0, 1, 2
 NBO_SCHED_COSINE, NBO_SCHED_LINEAR, NBO_SCHED_ONECYCLE, NBO_SCHED_STEP = 0, 1, 2, 3
 
 

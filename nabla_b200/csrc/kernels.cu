@@ -60,19 +60,26 @@ int32_t launch_sgd_f32(nbo_optimizer *h, uint32_t cb, uint32_t nc, const SgdHP &
     return launched(h);
 }
 
+template <bool kScaled, bool kGradF32>
+static int32_t launch_adam_mixed_one(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp,
+                                     const StepCtrl *ctrl, const AdamHP *hp_dev)
+{
+    int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<kScaled, kGradF32>);
+    adam_mixed_kernel<kScaled, kGradF32><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp,
+                                                                        ctrl, hp_dev);
+    return launched(h);
+}
+
 int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl)
 {
     if (nc == 0) return NBO_OK;
-    if (with_ctrl || hp.inv_scale != 1.0f) {
-        int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<true>);
-        adam_mixed_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp,
-                                                                with_ctrl ? h->d_ctrl : nullptr, nullptr);
-    } else {
-        int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<false>);
-        adam_mixed_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, hp, nullptr,
-                                                                 nullptr);
-    }
-    return launched(h);
+    const bool gf32 = h->precision == NBO_MIXED_BF16_F32GRAD;
+    const StepCtrl *ctrl = with_ctrl ? h->d_ctrl : nullptr;
+    if (with_ctrl || hp.inv_scale != 1.0f)
+        return gf32 ? launch_adam_mixed_one<true, true>(h, cb, nc, hp, ctrl, nullptr)
+                    : launch_adam_mixed_one<true, false>(h, cb, nc, hp, ctrl, nullptr);
+    return gf32 ? launch_adam_mixed_one<false, true>(h, cb, nc, hp, nullptr, nullptr)
+                : launch_adam_mixed_one<false, false>(h, cb, nc, hp, nullptr, nullptr);
 }
 
 template <bool kBf16, bool kCheckEach>
@@ -105,7 +112,8 @@ int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_nor
 int32_t launch_norm_dev(nbo_optimizer *h, const float *inv_scale_dev, double max_norm)
 {
     NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
-    launch_norm_one<true, true>(h, 1.0f, max_norm, 1, out, inv_scale_dev);
+    if (h->precision == NBO_MIXED_BF16_F32GRAD) launch_norm_one<false, true>(h, 1.0f, max_norm, 1, out, inv_scale_dev);
+    else launch_norm_one<true, true>(h, 1.0f, max_norm, 1, out, inv_scale_dev);
     return launched(h);
 }
 
@@ -125,10 +133,10 @@ int32_t launch_adam_mixed_dev(nbo_optimizer *h, uint32_t cb, uint32_t nc, int gr
 {
     if (nc == 0) return NBO_OK;
     AdamHP unused{};
-    int grid = grid_for(h, nc, (const void *)adam_mixed_kernel<true>);
-    adam_mixed_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks + cb, nc, unused,
-                                                            with_ctrl ? h->d_ctrl : nullptr, h->d_hp + group);
-    return launched(h);
+    const StepCtrl *ctrl = with_ctrl ? h->d_ctrl : nullptr;
+    return h->precision == NBO_MIXED_BF16_F32GRAD
+               ? launch_adam_mixed_one<true, true>(h, cb, nc, unused, ctrl, h->d_hp + group)
+               : launch_adam_mixed_one<true, false>(h, cb, nc, unused, ctrl, h->d_hp + group);
 }
 
 int32_t launch_finalize_ranks(nbo_optimizer *h, const double *gathered, int world, double max_norm)

@@ -98,7 +98,7 @@ int32_t build_table(nbo_optimizer *h)
     NBO_CUDA(h, cudaMalloc(&h->d_s1, state_bytes));
     NBO_CUDA(h, cudaMemsetAsync(h->d_s0, 0, state_bytes, h->stream));
     NBO_CUDA(h, cudaMemsetAsync(h->d_s1, 0, state_bytes, h->stream));
-    if (h->precision == NBO_MIXED_BF16) {
+    if (h->precision != NBO_F32) {
         NBO_CUDA(h, cudaMalloc(&h->d_s2, state_bytes));
         NBO_CUDA(h, cudaMemsetAsync(h->d_s2, 0, state_bytes, h->stream));
     }
@@ -142,6 +142,9 @@ static int32_t upload_descs(nbo_optimizer *h)
 int32_t bind_list(nbo_optimizer *h, uint64_t n, void *const *params, const void *const *grads,
                   int elem_size, const char *who)
 {
+    // element sizes of the two columns: equal except for bf16 params with fp32 gradients
+    const int p_es = elem_size;
+    const int g_es = (h->precision == NBO_MIXED_BF16_F32GRAD) ? 4 : elem_size;
     if (!h->configured)
         return fail(h, NBO_ERR_STATE, std::string("nabla-optim-b200: ") + who + " before set_tensors");
     if (h->zero1)
@@ -151,7 +154,7 @@ int32_t bind_list(nbo_optimizer *h, uint64_t n, void *const *params, const void 
         return fail(h, NBO_ERR_INVALID, std::string("nabla-train: ") + who + " params count mismatch");
     if (n && !params && !grads)
         return fail(h, NBO_ERR_INVALID, std::string("nabla-optim-b200: ") + who + ": null pointer list");
-    const uintptr_t vec_mask = elem_size == 4 ? 15u : 7u;
+    const uintptr_t p_mask = p_es == 4 ? 15u : 7u, g_mask = g_es == 4 ? 15u : 7u;
     bool changed = !h->table_bound;
     for (uint64_t t = 0; t < n && !changed; ++t) {
         if (params && h->bound_p[t] != params[t]) changed = true;
@@ -163,8 +166,8 @@ int32_t bind_list(nbo_optimizer *h, uint64_t n, void *const *params, const void 
         if ((params && !params[t]) || (grads && !grads[t]))
             return fail(h, NBO_ERR_INVALID, std::string("nabla-optim-b200: ") + who +
                                                 ": null device pointer for tensor " + std::to_string(t));
-        if ((params && ((uintptr_t)params[t] & (uintptr_t)(elem_size - 1))) ||
-            (grads && ((uintptr_t)grads[t] & (uintptr_t)(elem_size - 1))))
+        if ((params && ((uintptr_t)params[t] & (uintptr_t)(p_es - 1))) ||
+            (grads && ((uintptr_t)grads[t] & (uintptr_t)(g_es - 1))))
             return fail(h, NBO_ERR_INVALID, std::string("nabla-optim-b200: ") + who +
                                                 ": pointer not aligned to its element size, tensor " +
                                                 std::to_string(t));
@@ -175,8 +178,8 @@ int32_t bind_list(nbo_optimizer *h, uint64_t n, void *const *params, const void 
         TensorDesc &d = h->h_descs[t];
         if (params) { d.p = params[t]; h->bound_p[t] = params[t]; }
         if (grads) { d.g = grads[t]; h->bound_g[t] = grads[t]; }
-        bool aligned = (((uintptr_t)d.g & vec_mask) == 0) &&
-                       (d.p == nullptr || ((uintptr_t)d.p & vec_mask) == 0);
+        bool aligned = (((uintptr_t)d.g & g_mask) == 0) &&
+                       (d.p == nullptr || ((uintptr_t)d.p & p_mask) == 0);
         d.head = aligned ? 0u : 0xffffffffu;
     }
     return upload_descs(h);
@@ -398,13 +401,13 @@ int32_t nbo_set_tensors(nbo_optimizer *h, uint64_t n, const uint64_t *numel, con
     if (h->groups.empty())
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_set_tensors before any nbo_add_group");
     if (n && !numel) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null numel list");
-    if (precision != NBO_F32 && precision != NBO_MIXED_BF16)
+    if (precision != NBO_F32 && precision != NBO_MIXED_BF16 && precision != NBO_MIXED_BF16_F32GRAD)
         return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: unknown precision");
     for (uint64_t t = 0; t < n; ++t) {
         int32_t g = group_ids ? group_ids[t] : 0;
         if (g < 0 || (size_t)g >= h->groups.size())
             return fail(h, NBO_ERR_INVALID, "nabla-train: group assignment incomplete");
-        if (precision == NBO_MIXED_BF16 && h->groups[g].cfg.kind == NBO_SGD)
+        if (precision != NBO_F32 && h->groups[g].cfg.kind == NBO_SGD)
             return fail(h, NBO_ERR_INVALID,
                         "nabla-optim-b200: mixed precision supports Adam/AdamW groups only");
     }
@@ -612,7 +615,7 @@ int32_t nbo_zero_grad(nbo_optimizer *h, uint64_t n, void *const *grads)
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
     if (n && !grads) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null pointer list");
     DeviceGuard guard(h->device);
-    bool bf16 = h->precision == NBO_MIXED_BF16;
+    bool bf16 = h->precision == NBO_MIXED_BF16;  // the gradient column is bf16 only in this mode
     int32_t rc = bind_list(h, n, nullptr, (const void *const *)grads, bf16 ? 2 : 4, "zero_grad");
     if (rc != NBO_OK) return rc;
     return launch_zero_grads(h, bf16);
@@ -706,7 +709,7 @@ int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *grads, do
 int32_t nbo_init_master_from_params(nbo_optimizer *h, uint64_t n, const void *const *params_bf16)
 {
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
-    if (!h->configured || h->precision != NBO_MIXED_BF16)
+    if (!h->configured || h->precision == NBO_F32)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: masters exist only on mixed-precision handles");
     if (n && !params_bf16) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null pointer list");
     DeviceGuard guard(h->device);
@@ -721,7 +724,7 @@ int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
 {
     NBO_SYNC_STATE(h);
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
-    if (h->configured && h->precision != NBO_MIXED_BF16)
+    if (h->configured && h->precision == NBO_F32)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_step_mixed needs a mixed-precision handle");
     if (n && (!params_bf16 || !grads_bf16))
         return fail(h, NBO_ERR_INVALID, "nabla-train: params/grads length mismatch (null list)");
@@ -733,7 +736,7 @@ int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
     h->prof_norm_valid = false;
     if (checked) {
         prof_mark(h, 0);
-        rc = launch_norm(h, true, inv_scale, max_norm, 1);
+        rc = launch_norm(h, h->precision == NBO_MIXED_BF16, inv_scale, max_norm, 1);
         if (rc != NBO_OK) return rc;
         prof_mark(h, 1);
     }
@@ -755,7 +758,7 @@ int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *params_b
                              const void *const *grads_bf16, int32_t use_scaler, double max_norm)
 {
     if (!h) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null handle");
-    if (!h->configured || h->precision != NBO_MIXED_BF16 || h->zero1)
+    if (!h->configured || h->precision == NBO_F32 || h->zero1)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_step_mixed_async needs an unsharded mixed-precision handle");
     if (h->groups.size() > (size_t)kMaxDevGroups)
         return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: the asynchronous step supports at most 32 groups");

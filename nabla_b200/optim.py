@@ -630,14 +630,19 @@ class MixedAdamW:
     cast to bf16, in the order of Trainer::train_epoch_with_max_steps (trainer.rs:230-283)."""
 
     def __init__(self, names, shapes, groups: Sequence[ParamGroupConfig],
-                 default_group: Optional[ParamGroupConfig] = None, *, device=None, stream=None):
+                 default_group: Optional[ParamGroupConfig] = None, *, device=None, stream=None,
+                 grad_dtype: torch.dtype = torch.bfloat16):
+        """`grad_dtype=torch.float32` takes fp32 gradients (e.g. accumulated over micro-batches in fp32)
+        for the same bf16 params / fp32 master step."""
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
         self._configs, self._gid_of = kept, gid_of
+        self._grad_dtype = grad_dtype
         self._h = _Handle(device, stream)
         for cfg in kept:
             self._h.add_group(cfg.to_c())
-        self._h.set_tensors(self._numel, gid_of, L.NBO_MIXED_BF16)
+        self._h.set_tensors(self._numel, gid_of,
+                            L.NBO_MIXED_BF16 if grad_dtype == torch.bfloat16 else L.NBO_MIXED_BF16_F32GRAD)
 
     @classmethod
     def adamw(cls, lr, weight_decay, shapes, **kw):
@@ -661,7 +666,7 @@ class MixedAdamW:
         assert len(params) == len(grads), "nabla-train: AdamW params/grads length mismatch"
         assert len(params) == len(self._numel), "nabla-train: AdamW params count mismatch"
         _check_tensors(params, torch.bfloat16, "params")
-        _check_tensors(grads, torch.bfloat16, "grads")
+        _check_tensors(grads, self._grad_dtype, "grads")
         return self.step_ptrs(_ptrs(params), _ptrs(grads), use_scaler=use_scaler, max_norm=max_norm)
 
     def step_ptrs(self, params_arr, grads_arr, *, use_scaler=True, max_norm=0.0) -> StepOutcome:

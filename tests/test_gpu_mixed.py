@@ -221,3 +221,47 @@ def test_large_norm_and_exact_flag(nb):
         assert norm(g)[1] is True
         g[n - 2] = 0.0
     assert norm(g)[1] is False
+
+
+@pytest.mark.parametrize("offset", [0, 1])
+def test_fp32_gradient_variant_versus_oracle(nb, oracle, offset):
+    """bf16 params + fp32 gradients (accumulated in fp32): GradScaler -> clip -> AdamW on the masters -> cast,
+    composed from the oracle's f32 pieces; skip decisions and casts bit-exact, masters within 1e-5."""
+    rng = np.random.default_rng(21)
+    sizes = [1, 5, 4097, 70001]
+    w = [rng.normal(0, 0.02, n).astype(np.float32) for n in sizes]
+    m = [np.zeros(n, np.float32) for n in sizes]
+    v = [np.zeros(n, np.float32) for n in sizes]
+    sc = oracle.new_scaler()
+    opt = nb.MixedAdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], grad_dtype=torch.float32)
+
+    def alloc(n, dt):
+        return torch.zeros(n + 8, dtype=dt, device="cuda")[offset:offset + n]
+    dp = [alloc(n, torch.bfloat16) for n in sizes]
+    dg = [alloc(n, torch.float32) for n in sizes]
+    for i, a in enumerate(w):
+        opt.load_master(i, torch.from_numpy(a))
+        dp[i].copy_(bf16_dev(oracle.bf16_from_f32(a)))
+    t_adam = 0
+    for step in range(6):
+        gs = [(rng.normal(0, 1e-4, n) * sc.scale).astype(np.float32) for n in sizes]
+        if step == 2:
+            gs[3][4242] = np.nan
+        for d, g in zip(dg, gs):
+            d.copy_(torch.from_numpy(g))
+        res = opt.step(dp, dg, use_scaler=True, max_norm=0.004)
+        ok = oracle.scaler_unscale_and_update(sc, gs)
+        assert res.applied == ok and res.loss_scale == sc.scale
+        if ok:
+            norm = oracle.clip_grad_norm(gs, 0.004)
+            assert abs(res.grad_norm - norm) <= 1e-12 * norm
+            t_adam += 1
+            for i in range(len(sizes)):
+                oracle.adam_step(w[i], gs[i], m[i], v[i], 3e-4, weight_decay=0.1, step=t_adam, decoupled=True)
+    assert opt.step_count() == t_adam == 5
+    for i, n in enumerate(sizes):
+        gw = opt.master(i).numpy()
+        assert_close_rel(gw, w[i], f"master n={n}")
+        assert np.array_equal(bf16_bits(dp[i]), oracle.bf16_from_f32(gw))
+    with pytest.raises(TypeError):
+        opt.step(dp, [x.to(torch.bfloat16) for x in dg])
