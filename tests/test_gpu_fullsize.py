@@ -157,3 +157,47 @@ def test_llama1b_mixed_full_size_properties(nb, oracle):
     assert not r2.applied and r2.nonfinite and r2.loss_scale == 32768.0 and r2.step_count == 1
     assert pflat.view(torch.int16).to(torch.int64).sum().item() == digest_p
     assert torch.equal(opt._h.state_export(146, 0, sizes[146]), m_before)
+
+
+def test_single_tensor_beyond_2_to_32_elements(nb, oracle):
+    """One bf16 tensor of 2^32 + 4101 elements (69 GB with its state): offsets need 64 bits, the chunk list has
+    more than a million entries and ends in a partial chunk with a tail.  Slices around 0, 2^31, 2^32 and the
+    end follow the oracle; untouched guard elements past the end stay untouched."""
+    n = (1 << 32) + 4101
+    free, _ = torch.cuda.mem_get_info()
+    if free < 80 * (1 << 30):
+        pytest.skip("needs 80 GB of free device memory")
+    guard = 64
+    p = torch.empty(n + guard, dtype=torch.bfloat16, device="cuda")
+    g = torch.empty(n + guard, dtype=torch.bfloat16, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    for off in range(0, n + guard, 1 << 28):
+        m = min(1 << 28, n + guard - off)
+        p[off:off + m] = torch.randn(m, device="cuda", generator=gen) * 0.02
+        g[off:off + m] = torch.randn(m, device="cuda", generator=gen) * 1e-3
+    p_guard = p[n:].clone()
+    opt = nb.MixedAdamW.adamw(1e-3, 0.1, [(n,)])
+    pv, gv = p[:n], g[:n]
+    opt.init_master_from_params([pv])
+    windows = [(0, 3000), ((1 << 31) - 1500, 3000), ((1 << 32) - 2000, 4000), (n - 3000, 3000)]
+    before = [(pv[a:a + k].float().cpu().numpy(), gv[a:a + k].float().cpu().numpy()) for a, k in windows]
+    res = opt.step([pv], [gv], use_scaler=False, max_norm=0.0)
+    assert res.applied and opt.step_count() == 1
+    assert opt._h.table_info()[1] == (n + 4095) // 4096
+    for (a, k), (w0, g0) in zip(windows, before):
+        w, m, v = w0.copy(), np.zeros(k, np.float32), np.zeros(k, np.float32)
+        oracle.adam_step(w, g0, m, v, 1e-3, weight_decay=0.1, step=1, decoupled=True)
+        got = bf16_bits(pv[a:a + k])
+        want = oracle.bf16_from_f32(w)
+        assert float((got == want).mean()) > 0.999, f"window at {a}"
+        assert np.abs(oracle.bf16_to_f32(got) - oracle.bf16_to_f32(want)).max() <= np.abs(w).max() * 2 ** -7
+    assert torch.equal(p[n:].view(torch.int16), p_guard.view(torch.int16))
+    # the norm pass over the same tensor: 64-bit offsets there too
+    import ctypes as C
+    a_, b_ = C.c_double(), C.c_int32()
+    opt._h.check(opt._h.lib.nbo_grad_norm(opt._h.h, 1, nb._lib.ptr_array([gv.data_ptr()]), C.byref(a_), C.byref(b_)))
+    want = 0.0
+    for off in range(0, n, 1 << 28):
+        m = min(1 << 28, n - off)
+        want += float((gv[off:off + m].double() ** 2).sum())
+    assert not b_.value and abs(a_.value - want ** 0.5) <= 1e-11 * want ** 0.5
