@@ -201,3 +201,35 @@ def test_single_tensor_beyond_2_to_32_elements(nb, oracle):
         m = min(1 << 28, n - off)
         want += float((gv[off:off + m].double() ** 2).sum())
     assert not b_.value and abs(a_.value - want ** 0.5) <= 1e-11 * want ** 0.5
+
+
+def test_mixed_64m_element_slice_20_steps_against_oracle(nb, oracle):
+    """A 64 Mi-element tensor (the size class of the large matrices of the 8 G-parameter list) through 20
+    mixed-precision steps with loss scaling, an injected overflow and clipping, against the oracle element
+    for element: decisions and loss scale exact, masters / m / v within 1e-5, bf16 params = cast of masters."""
+    n = (1 << 26) + 3
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    w0 = (torch.randn(n, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    p = w0.clone()
+    opt = nb.MixedAdamW.adamw(3e-4, 0.1, [(n,)])
+    opt.init_master_from_params([p])
+    mo = oracle.MixedOracle([w0.float().cpu().numpy()], [oracle.AdamCfg(3e-4, 0.9, 0.999, 1e-8, 0.1, 1)])
+    for step in range(20):
+        g = (torch.randn(n, device="cuda", generator=gen) * (1e-4 * mo.scaler.scale)).to(torch.bfloat16)
+        if step == 7:
+            g[n - 2] = float("-inf")
+        res = opt.step([p], [g], use_scaler=True, max_norm=0.5)
+        ok, norm = mo.step([bf16_bits(g)], max_norm=0.5)
+        assert res.applied == ok and res.loss_scale == mo.scaler.scale and res.step_count == mo.step_count.value
+        if ok:   # the reference's serial f64 sum over 6.7e7 squares carries ~1e-12 of rounding itself
+            assert abs(res.grad_norm - norm) <= 1e-10 * norm
+    assert opt.step_count() == 19
+    gw = opt.master(0).numpy()
+    gm, gv = opt.moments(0)
+    assert_close_rel(gw, mo.master[0], "master")
+    assert_close_rel(gm.numpy(), mo.m[0], "m")
+    assert_close_rel(gv.numpy(), mo.v[0], "v")
+    assert np.array_equal(bf16_bits(p), oracle.bf16_from_f32(gw))
+    same = float((bf16_bits(p) == mo.p[0]).mean())
+    print(f"64 Mi slice, 19 applied steps: {100 * same:.4f}% of bf16 params equal the oracle's")
+    assert same > 0.999
