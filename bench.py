@@ -282,10 +282,25 @@ def run_ours(args, wl_name, wl):
         padded, shard = opt.padded, opt.shard
         fused = world > 1 and args.zero1_path != "nccl"
         if fused:
-            # buckets in symmetric memory; the collectives are fused into the update kernels
+            # buckets in symmetric memory; the collectives are fused into the update kernels.  If the fabric
+            # or the runtime cannot provide symmetric memory on some rank, every rank falls back to the
+            # NCCL-around-the-update path together and the line says so.
             tr = {"auto": 0, "peer": 1, "mcast": 2}[args.zero1_path]
-            pflat, gflat = opt.attach_symmetric(transport=tr)
-        else:
+            ok = 1
+            try:
+                pflat, gflat = opt.attach_symmetric(transport=tr)
+            except Exception as exc:                       # noqa: BLE001 - any failure means "not available"
+                ok = 0
+                extra["fused_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+            agree = torch.tensor([ok], device=dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            if int(agree.item()) == 0:
+                fused = False
+                del opt
+                torch.cuda.empty_cache()
+                uid = nb.exchange_unique_id(rank, world)
+                opt = nb.Zero1AdamW.adamw(wl["lr"], wl["wd"], shapes, rank, world, uid)
+        if not fused:
             pflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
             gflat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
         fill_randn_bf16(pflat[:total], 0.02, torch.Generator(device=dev).manual_seed(7))
@@ -297,6 +312,8 @@ def run_ours(args, wl_name, wl):
         else:
             step = lambda: opt.step_ptrs(pp, gp, average=True, use_scaler=False, max_norm=0.0)
         extra["zero1_path"] = ("fused-" + args.zero1_path) if fused else ("nccl" if world > 1 else "local")
+        if fused:
+            extra["zero1_transport"] = "mcast" if (tr == 2 or (tr == 0 and world >= 4 and opt.has_multicast)) else "peer"
         handle = opt._h
         b, e, _ = opt.shard_range()
         local_elems = max(0, min(e, total) - b)
@@ -489,9 +506,7 @@ def run_ours(args, wl_name, wl):
     if wl["kind"] == "zero1" and world > 1:
         # bytes that must cross NVLink per GPU and direction for one step, against the measured 770 GB/s peer copy
         bucket = 2.0 * padded
-        path = extra.get("zero1_path", "")
-        tr = "mcast" if (path == "fused-mcast" or (path == "fused-auto" and world >= 4)) else (
-            "peer" if path.startswith("fused") else "nccl")
+        tr = extra.get("zero1_transport", "nccl")
         per_dir = bucket * (1.0 + 1.0 / world) if tr == "mcast" else 2.0 * bucket * (world - 1) / world
         step_s = dev_s / args.steps
         line["nvlink"] = {"transport": tr, "bytes_per_gpu_per_direction": per_dir, "peak": 770.0, "unit": "GB/s",
