@@ -253,3 +253,45 @@ def test_powf_half_versus_sqrt_rate(oracle):
     ulp = np.abs(pw.view(np.int32).astype(np.int64) - sq.view(np.int32).astype(np.int64))
     assert ulp.max() <= 1
     assert (ulp != 0).mean() < 0.05
+
+
+def test_adam_and_adamw_against_an_independent_implementation(oracle):
+    """The reference's tests do not pin Adam/AdamW values, so the restatement is cross-checked against a second,
+    independently written implementation of the same published update (torch.optim, float64): the f64 oracle
+    must agree to rounding noise and the f32 oracle to f32 precision, over 50 steps."""
+    import torch
+    rng = np.random.default_rng(42)
+    n = 2000
+    p0 = rng.normal(0, 0.5, n)
+    grads = rng.normal(0, 1e-2, (50, n))
+    for decoupled, cls, kw in ((False, torch.optim.Adam, {}), (True, torch.optim.AdamW, dict(weight_decay=0.05))):
+        tp = torch.nn.Parameter(torch.tensor(p0, dtype=torch.float64))
+        topt = cls([tp], lr=1e-3, betas=(0.9, 0.999), eps=1e-8, **kw)
+        p64, m64, v64 = p0.copy(), np.zeros(n), np.zeros(n)
+        p32, m32, v32 = p0.astype(np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        for t in range(50):
+            tp.grad = torch.tensor(grads[t])
+            topt.step()
+            oracle.adam_step(p64, grads[t].copy(), m64, v64, 1e-3, weight_decay=kw.get("weight_decay", 0.0), step=t + 1,
+                             decoupled=decoupled)
+            oracle.adam_step(p32, grads[t].astype(np.float32), m32, v32, 1e-3,
+                             weight_decay=kw.get("weight_decay", 0.0), step=t + 1, decoupled=decoupled)
+        want = tp.detach().numpy()
+        assert np.max(np.abs(p64 - want)) < 1e-12
+        assert np.max(np.abs(p32.astype(np.float64) - want)) < 5e-6
+
+
+def test_sgd_momentum_against_an_independent_implementation(oracle):
+    import torch
+    rng = np.random.default_rng(43)
+    n = 1000
+    p0 = rng.normal(0, 0.5, n)
+    grads = rng.normal(0, 1e-2, (30, n))
+    tp = torch.nn.Parameter(torch.tensor(p0, dtype=torch.float64))
+    topt = torch.optim.SGD([tp], lr=0.1, momentum=0.9, weight_decay=0.01)      # no dampening, no Nesterov
+    p, vel = p0.copy(), np.zeros(n)
+    for t in range(30):
+        tp.grad = torch.tensor(grads[t])
+        topt.step()
+        oracle.sgd_step(p, grads[t].copy(), vel, 0.1, 0.9, 0.01)
+    assert np.max(np.abs(p - tp.detach().numpy())) < 1e-12
