@@ -75,6 +75,9 @@ WORKLOADS = {
     "llama1b_mixed": dict(kind="mixed", shapes=lambda: llama_shapes(2048, 16, 8192, 32000, 2048),
                           lr=3e-4, wd=0.1, bytes_per_elem=30, use_scaler=True, max_norm=1.0,
                           desc="Llama-1B-shaped mixed AdamW with dynamic loss scale and clip 1.0"),
+    "llama1b_scaler": dict(kind="mixed", shapes=lambda: llama_shapes(2048, 16, 8192, 32000, 2048),
+                           lr=3e-4, wd=0.1, bytes_per_elem=30, use_scaler=True, max_norm=0.0,
+                           desc="Llama-1B-shaped mixed AdamW with dynamic loss scale, no clipping (flag-only pre-pass)"),
     "mixed_small": dict(kind="mixed", shapes=lambda: llama_shapes(2048, 2, 8192, 16000, 2048),
                         lr=3e-4, wd=0.1, bytes_per_elem=30, use_scaler=True, max_norm=1.0,
                         desc="2-layer slice of the Llama-1B shapes (0.2 G params, 3.2 GB): the small case for ncu"),

@@ -104,7 +104,8 @@ typedef struct {
 typedef struct {
     int32_t applied;      /* 1 = update applied, 0 = skipped (non-finite grads)       */
     int32_t nonfinite;    /* 1 = a non-finite gradient was seen                        */
-    double grad_norm;     /* pre-clip global L2 norm of the unscaled grads (0 if none) */
+    double grad_norm;     /* pre-clip global L2 norm of the unscaled grads; 0 when
+                             max_norm <= 0 (no norm is taken then, trainer.rs:501-503) */
     double loss_scale;    /* scale to use for the NEXT backward pass                   */
     uint64_t step_count;  /* optimizer step count after this call (group 0)            */
 } nbo_step_result;

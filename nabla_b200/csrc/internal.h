@@ -137,6 +137,7 @@ int32_t launch_scale_grads(nbo_optimizer *h, int mode, float factor);
 int32_t launch_zero_grads(nbo_optimizer *h, bool bf16);
 int32_t launch_init_master(nbo_optimizer *h);
 int32_t launch_accumulate(nbo_optimizer *h);
+int32_t launch_nonfinite(nbo_optimizer *h, bool bf16);  // flag only, no norm (writes the decision record)
 int32_t launch_norm_dev(nbo_optimizer *h, const float *inv_scale_dev, double max_norm);
 int32_t launch_prepare(nbo_optimizer *h, int use_scaler);
 int32_t launch_commit(nbo_optimizer *h, bool checked, int use_scaler);

@@ -111,6 +111,20 @@ int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_nor
     return launched(h);
 }
 
+int32_t launch_nonfinite(nbo_optimizer *h, bool bf16)
+{
+    NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
+    uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;
+    if (bf16) {
+        int grid = grid_for(h, units, (const void *)nonfinite_kernel<true>);
+        nonfinite_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, out);
+    } else {
+        int grid = grid_for(h, units, (const void *)nonfinite_kernel<false>);
+        nonfinite_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, out);
+    }
+    return launched(h);
+}
+
 // Asynchronous step: the unscale factor is read from device memory, so the per-element flag test is kept
 // (the host cannot know whether the factor exceeds 1).
 int32_t launch_norm_dev(nbo_optimizer *h, const float *inv_scale_dev, double max_norm)

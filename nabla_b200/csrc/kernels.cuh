@@ -622,6 +622,106 @@ norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chun
     }
 }
 
+// Non-finite test alone, for steps that use loss scaling but no clipping: no norm is needed then, only the
+// all-or-nothing skip decision, and without the f64 squares the pass is a plain HBM read.  The exponent
+// field is all ones exactly when adding one to it carries into the (masked-out) sign position, so a whole
+// 32-bit word - two bf16 values or one f32 - is tested with an AND, an ADD and an OR.
+template <bool kBf16>
+__global__ void __launch_bounds__(kBlock)
+nonfinite_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks, uint32_t nchunks,
+                 NormOut out)
+{
+    constexpr uint32_t kMask = kBf16 ? 0x7f807f80u : 0x7f800000u;
+    constexpr uint32_t kOne = kBf16 ? 0x00800080u : 0x00800000u;
+    uint32_t accw = 0;
+    const uint32_t stride = gridDim.x * kNormBatch;
+    for (uint32_t c0 = blockIdx.x * kNormBatch; c0 < nchunks; c0 += stride) {
+        const char *base[kNormBatch];
+        uint32_t nitems[kNormBatch];
+        bool stray = false;
+#pragma unroll
+        for (int j = 0; j < kNormBatch; ++j) {
+            nitems[j] = 0;
+            base[j] = nullptr;
+            if (c0 + j < nchunks) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                base[j] = (const char *)d.g + cv.item0 * (kBf16 ? 2 : 4);
+                nitems[j] = cv.nitems;
+                stray |= (cv.s_lo1 > cv.s_lo0) | (cv.s_hi1 > cv.s_hi0);
+            }
+        }
+        if (kBf16) {
+            uint2 g[kNormBatch][kItemsPerThread];
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    g[j][u] = i < nitems[j] ? ld_stream((const uint2 *)base[j] + i) : make_uint2(0u, 0u);
+                }
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u)
+                    accw |= ((g[j][u].x & kMask) + kOne) | ((g[j][u].y & kMask) + kOne);
+        } else {
+            float4 g[kNormBatch][kItemsPerThread];
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    g[j][u] = i < nitems[j] ? ld_stream((const float4 *)base[j] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+            for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u)
+                    accw |= ((__float_as_uint(g[j][u].x) & kMask) + kOne) | ((__float_as_uint(g[j][u].y) & kMask) + kOne) |
+                            ((__float_as_uint(g[j][u].z) & kMask) + kOne) | ((__float_as_uint(g[j][u].w) & kMask) + kOne);
+        }
+        if (stray) {
+            for (int j = 0; j < kNormBatch && c0 + j < nchunks; ++j) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                for (int r = 0; r < 2; ++r) {
+                    uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+                    for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                        float gi = kBf16 ? bf16_to_f32(((const uint16_t *)d.g)[i]) : ((const float *)d.g)[i];
+                        accw |= is_nonfinite(gi) ? 0x80000000u : 0u;
+                    }
+                }
+            }
+        }
+    }
+    int bad = (accw & 0x80008000u) != 0u ? 1 : 0;
+    double zero = 0.0;
+    block_sum_f64(zero, bad);
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) {
+        out.partial_bad[blockIdx.x] = bad;
+        __threadfence();
+        uint32_t t = atomicInc(out.ticket, gridDim.x - 1);
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    int anybad = 0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kBlock) anybad |= __ldcg(out.partial_bad + i);
+    zero = 0.0;
+    block_sum_f64(zero, anybad);
+    if (threadIdx.x == 0) {
+        out.local[0] = 0.0;
+        out.local[1] = anybad ? 1.0 : 0.0;
+        write_ctrl(out.ctrl, 0.0, anybad, 0.0);
+    }
+}
+
 // Cross-rank finalize: `gathered` holds {sumsq, nonfinite} of every rank in
 // rank order; every rank adds them in that order and so reaches the same
 // decision bit for bit.

@@ -736,7 +736,10 @@ int32_t nbo_step_mixed(nbo_optimizer *h, uint64_t n, void *const *params_bf16,
     h->prof_norm_valid = false;
     if (checked) {
         prof_mark(h, 0);
-        rc = launch_norm(h, h->precision == NBO_MIXED_BF16, inv_scale, max_norm, 1);
+        // loss scaling without clipping needs the skip decision only (clip_grad_norm is then not run and
+        // reports 0, trainer.rs:501-503): the flag-only pass is a plain HBM read
+        rc = max_norm > 0.0 ? launch_norm(h, h->precision == NBO_MIXED_BF16, inv_scale, max_norm, 1)
+                            : launch_nonfinite(h, h->precision == NBO_MIXED_BF16);
         if (rc != NBO_OK) return rc;
         prof_mark(h, 1);
     }
@@ -782,7 +785,8 @@ int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *params_b
     rc = launch_prepare(h, use_scaler);
     if (rc != NBO_OK) return rc;
     if (checked) {
-        rc = launch_norm_dev(h, h->d_inv_scale, max_norm);
+        rc = max_norm > 0.0 ? launch_norm_dev(h, h->d_inv_scale, max_norm)
+                            : launch_nonfinite(h, h->precision == NBO_MIXED_BF16);
         if (rc != NBO_OK) return rc;
     }
     for (size_t g = 0; g < h->groups.size(); ++g) {

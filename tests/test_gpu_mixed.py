@@ -265,3 +265,28 @@ def test_fp32_gradient_variant_versus_oracle(nb, oracle, offset):
         assert np.array_equal(bf16_bits(dp[i]), oracle.bf16_from_f32(gw))
     with pytest.raises(TypeError):
         opt.step(dp, [x.to(torch.bfloat16) for x in dg])
+
+
+@pytest.mark.parametrize("grad_dtype", [torch.bfloat16, torch.float32])
+def test_loss_scaling_without_clipping_uses_the_flag_only_pass(nb, oracle, grad_dtype):
+    """use_scaler with max_norm = 0: no norm is taken (grad_norm reports 0 like clip_grad_norm with max_norm <= 0),
+    yet a non-finite gradient at any position - vector body, stray head / tail, first or last tensor - skips."""
+    sizes = [5, 3 * 4096 + 3, 4096, 70001]
+    opt = nb.MixedAdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], grad_dtype=grad_dtype)
+    p = [(torch.randn(n, device="cuda") * 0.02).to(torch.bfloat16) for n in sizes]
+    opt.init_master_from_params(p)
+    g = [(torch.randn(n, device="cuda") * 6.0).to(grad_dtype) for n in sizes]
+    res = opt.step(p, g, use_scaler=True, max_norm=0.0)
+    assert res.applied and res.grad_norm == 0.0 and res.step_count == 1
+    scale = res.loss_scale
+    for t, pos in ((0, 0), (0, 4), (1, 0), (1, 4095), (1, 4096), (1, 3 * 4096 + 2), (2, 4095), (3, 70000), (3, 33333)):
+        for bad in (float("inf"), float("-inf"), float("nan")):
+            keep = g[t][pos].clone()
+            g[t][pos] = bad
+            res = opt.step(p, g, use_scaler=True, max_norm=0.0)
+            assert not res.applied and res.nonfinite and res.loss_scale == scale * 0.5, (t, pos, bad)
+            scale = res.loss_scale
+            g[t][pos] = keep
+    g[1][100] = 3.0e38 if grad_dtype == torch.float32 else 3.0e38          # huge but finite: not flagged
+    res = opt.step(p, g, use_scaler=True, max_norm=0.0)
+    assert res.applied and not res.nonfinite and res.step_count == 2
