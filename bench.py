@@ -81,6 +81,9 @@ WORKLOADS = {
     "mixed_small": dict(kind="mixed", shapes=lambda: llama_shapes(2048, 2, 8192, 16000, 2048),
                         lr=3e-4, wd=0.1, bytes_per_elem=30, use_scaler=True, max_norm=1.0,
                         desc="2-layer slice of the Llama-1B shapes (0.2 G params, 3.2 GB): the small case for ncu"),
+    "mixed_small_scaler": dict(kind="mixed", shapes=lambda: llama_shapes(2048, 2, 8192, 16000, 2048),
+                               lr=3e-4, wd=0.1, bytes_per_elem=30, use_scaler=True, max_norm=0.0,
+                               desc="mixed_small with loss scaling only (flag-only pre-pass): small case for ncu"),
     "gpt2_adam": dict(kind="f32", opt="adam", shapes=gpt2_shapes, lr=1e-3, bytes_per_elem=28,
                       desc="GPT-2-small-shaped fp32 Adam"),
     "frag_adamw": dict(kind="f32", opt="adamw", shapes=frag_sizes, lr=1e-3, wd=0.01, bytes_per_elem=28,
