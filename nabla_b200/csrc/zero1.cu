@@ -104,7 +104,8 @@ static void abort_comm(Zero1 *z)
 static int32_t nccl_wait(nbo_optimizer *h, Zero1 *z, ncclResult_t r, const char *what)
 {
     NcclApi *a = nccl_api();
-    const auto deadline = Clock::now() + std::chrono::duration<double>(z->timeout_s);
+    const auto start = Clock::now();
+    const auto deadline = start + std::chrono::duration<double>(z->timeout_s);
     while (r == ncclSuccess || r == ncclInProgress) {
         ncclResult_t st = ncclSuccess;
         ncclResult_t q = a->CommGetAsyncError(z->comm, &st);
@@ -117,7 +118,9 @@ static int32_t nccl_wait(nbo_optimizer *h, Zero1 *z, ncclResult_t r, const char 
                                                 std::to_string(z->timeout_s) + " s in " + what +
                                                 " (a rank did not arrive); communicator aborted");
         }
-        std::this_thread::sleep_for(std::chrono::microseconds(50));
+        // an enqueue normally completes within microseconds: spin first, back off only when it drags on
+        if (Clock::now() - start < std::chrono::milliseconds(2)) std::this_thread::yield();
+        else std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
     abort_comm(z);
     return fail_nccl(h, r, what);
