@@ -268,6 +268,79 @@ private:
     size_t ngroups_ = 0;
 };
 
+// ---- mixed precision -------------------------------------------------------------------------------
+// bf16 params and grads owned by the caller, fp32 master / m / v owned by the optimizer.  The reference has
+// no such type (its Optimizer has one scalar type); one step is GradScaler::unscale_and_update ->
+// clip_grad_norm -> AdamW<f32>::step on the masters -> cast to bf16, in the order of
+// Trainer::train_epoch_with_max_steps (trainer.rs:230-283).
+class MixedAdamW {
+public:
+    MixedAdamW(double lr, double weight_decay, const Shapes &shapes, int device = 0, void *stream = nullptr)
+        : handle_(std::make_shared<detail::Handle>(device, stream))
+    {
+        nbo_group_config c{NBO_ADAMW, lr, 0.9, 0.999, 1e-8, weight_decay, 0};
+        detail::check(h(), nbo_add_group(h(), &c, nullptr));
+        for (auto &s : shapes) numel_.push_back((uint64_t)s.first * s.second);
+        detail::check(h(), nbo_set_tensors(h(), numel_.size(), numel_.data(), nullptr, NBO_MIXED_BF16));
+    }
+    void init_master_from_params(const std::vector<Tensor *> &params_bf16)
+    {
+        std::vector<const void *> p;
+        for (auto *t : params_bf16) p.push_back(t->device_ptr);
+        detail::check(h(), nbo_init_master_from_params(h(), p.size(), p.data()));
+    }
+    // Synchronous step: returns the outcome (applied / skipped, pre-clip norm, next loss scale).
+    nbo_step_result step(const std::vector<Tensor *> &params_bf16, const std::vector<const Tensor *> &grads_bf16,
+                         bool use_scaler = true, double max_norm = 0.0)
+    {
+        collect_ptrs(params_bf16, grads_bf16);
+        nbo_step_result r{};
+        detail::check(h(), nbo_step_mixed(h(), p_.size(), p_.data(), g_.data(), use_scaler, max_norm, &r));
+        return r;
+    }
+    // Enqueue only; optimizer and scaler state advance on the device (graph-capturable).
+    void step_async(const std::vector<Tensor *> &params_bf16, const std::vector<const Tensor *> &grads_bf16,
+                    bool use_scaler = true, double max_norm = 0.0)
+    {
+        collect_ptrs(params_bf16, grads_bf16);
+        detail::check(h(), nbo_step_mixed_async(h(), p_.size(), p_.data(), g_.data(), use_scaler, max_norm));
+    }
+    nbo_step_result collect(uint64_t *steps_done = nullptr)
+    {
+        nbo_step_result r{};
+        detail::check(h(), nbo_step_mixed_collect(h(), &r, steps_done));
+        return r;
+    }
+    void set_lr(double lr) { detail::check(h(), nbo_set_lr(h(), lr)); }
+    uint64_t step_count() const
+    {
+        uint64_t c = 0;
+        detail::check(h(), nbo_step_count(h(), 0, &c));
+        return c;
+    }
+    std::vector<float> master(size_t tensor) const
+    {
+        std::vector<float> out(numel_.at(tensor));
+        detail::check(h(), nbo_state_export(h(), tensor, 2, out.data()));
+        return out;
+    }
+
+private:
+    nbo_optimizer *h() const { return handle_->h; }
+    void collect_ptrs(const std::vector<Tensor *> &p, const std::vector<const Tensor *> &g)
+    {
+        if (p.size() != g.size()) throw std::logic_error("nabla-train: AdamW params/grads length mismatch");
+        if (p.size() != numel_.size()) throw std::logic_error("nabla-train: AdamW params count mismatch");
+        p_.clear(); g_.clear();
+        for (auto *t : p) p_.push_back(t->device_ptr);
+        for (auto *t : g) g_.push_back(t->device_ptr);
+    }
+    std::shared_ptr<detail::Handle> handle_;
+    std::vector<uint64_t> numel_;
+    std::vector<void *> p_;
+    std::vector<const void *> g_;
+};
+
 // ---- schedules (core.rs:81-173) ---------------------------------------------------------------
 
 struct LrSchedule {

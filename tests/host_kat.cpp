@@ -3,6 +3,8 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
+#include <vector>
 #include <cuda_runtime.h>
 
 #include "../nabla_b200/host/nabla_optim.hpp"
@@ -89,6 +91,31 @@ int main()
             threw = std::string(e.what()) == "nabla-train: AdamW params count mismatch";
         }
         REQUIRE(threw);
+    }
+    {   // mixed precision through the C++ mirror: applied step, overflow skip, asynchronous step
+        auto bf16 = [](float f) { uint32_t u; std::memcpy(&u, &f, 4); return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16); };
+        auto unbf16 = [](uint16_t hbits) { uint32_t u = (uint32_t)hbits << 16; float f; std::memcpy(&f, &u, 4); return f; };
+        const size_t n = 4099;
+        std::vector<uint16_t> hp(n, bf16(1.0f)), hg(n, bf16(0.5f * 65536.0f));
+        Tensor p, g; p.rows = g.rows = 1; p.cols = g.cols = n;
+        REQUIRE(cudaMalloc(&p.device_ptr, n * 2) == cudaSuccess && cudaMalloc(&g.device_ptr, n * 2) == cudaSuccess);
+        REQUIRE(cudaMemcpy(p.device_ptr, hp.data(), n * 2, cudaMemcpyHostToDevice) == cudaSuccess);
+        REQUIRE(cudaMemcpy(g.device_ptr, hg.data(), n * 2, cudaMemcpyHostToDevice) == cudaSuccess);
+        MixedAdamW opt(0.1, 0.0, {{1, n}});
+        opt.init_master_from_params({&p});
+        nbo_step_result r = opt.step({&p}, {&g}, true, 0.0);
+        REQUIRE(r.applied == 1 && r.loss_scale == 65536.0 && r.step_count == 1);
+        REQUIRE(cudaMemcpy(hp.data(), p.device_ptr, n * 2, cudaMemcpyDeviceToHost) == cudaSuccess);
+        REQUIRE(std::fabs(unbf16(hp[0]) - 0.9f) < 4e-3f && hp[0] == hp[n - 1]);   // first Adam step moves by lr
+        hg[n - 1] = 0x7f80;                                                          // +inf: the step must be skipped
+        REQUIRE(cudaMemcpy(g.device_ptr, hg.data(), n * 2, cudaMemcpyHostToDevice) == cudaSuccess);
+        r = opt.step({&p}, {&g}, true, 0.0);
+        REQUIRE(r.applied == 0 && r.nonfinite == 1 && r.loss_scale == 32768.0 && r.step_count == 1);
+        opt.step_async({&p}, {&g}, true, 0.0);                                      // still +inf: skipped on the device
+        uint64_t done = 0;
+        r = opt.collect(&done);
+        REQUIRE(done == 1 && r.applied == 0 && r.loss_scale == 16384.0 && opt.step_count() == 1);
+        REQUIRE(std::fabs(opt.master(0)[5] - 0.9f) < 1e-6f);
     }
     std::printf("HOST_KAT_OK\n");
     return 0;

@@ -450,3 +450,15 @@ def test_adamw_step_free_function(nb, oracle, n):
         assert np.array_equal(bits(dm), bits(m)) and np.array_equal(bits(dv), bits(v))
         assert_close_rel(dp, p, f"n={n} off={off}")
         assert not base[0][off + n:].any() and not base[2][:off].any()       # nothing outside the tensor is touched
+
+
+def test_device_timing_api(nb):
+    n = 1 << 22
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    opt = nb.AdamW(1e-3, [(n,)])
+    with pytest.raises(nb._lib.NablaOptimError, match="profiling is off"):
+        opt._h.profile_last()
+    opt._h.profile(True)
+    opt.step([p], [g])
+    norm_ms, upd_ms = opt._h.profile_last()
+    assert norm_ms == 0.0 and 0.005 < upd_ms < 5.0
