@@ -54,6 +54,10 @@ __device__ __forceinline__ uint32_t scale_round_bf16(float sum, const PeerArgs &
 }
 
 // One item (4 bf16) of this rank's shard, reduced over all ranks.
+// Peer accesses carry no cache hint either: plain and .cs measured within 0.5 % at N = 2.
+__device__ __forceinline__ uint2 ld_peer(const uint2 *p) { return *p; }
+__device__ __forceinline__ void st_peer(uint2 *p, uint2 v) { *p = v; }
+
 template <int kT>
 __device__ __forceinline__ uint2 reduce_item(const uint2 *g_local, const PeerArgs &pa)
 {
@@ -69,7 +73,7 @@ __device__ __forceinline__ uint2 reduce_item(const uint2 *g_local, const PeerArg
     uint2 x[kMaxPeers];
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
-        if (r < pa.world) x[r] = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+        if (r < pa.world) x[r] = ld_peer((const uint2 *)((const char *)g_local + pa.g_peer[r]));
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
         if (r < pa.world) {
@@ -98,7 +102,7 @@ __device__ __forceinline__ void peer_prefetch(PeerItem &it, const uint2 *g_local
 {
 #pragma unroll
     for (int r = 0; r < kPrefetchRanks; ++r)
-        if (r < pa.world) it.x[r] = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+        if (r < pa.world) it.x[r] = ld_peer((const uint2 *)((const char *)g_local + pa.g_peer[r]));
 }
 
 __device__ __forceinline__ uint2 peer_reduce(const PeerItem &it, const uint2 *g_local, const PeerArgs &pa)
@@ -113,7 +117,7 @@ __device__ __forceinline__ uint2 peer_reduce(const PeerItem &it, const uint2 *g_
             a3 = __fadd_rn(a3, bf16_to_f32(it.x[r].y >> 16));
         }
     for (int r = kPrefetchRanks; r < pa.world; ++r) {
-        uint2 x = __ldcs((const uint2 *)((const char *)g_local + pa.g_peer[r]));
+        uint2 x = ld_peer((const uint2 *)((const char *)g_local + pa.g_peer[r]));
         a0 = __fadd_rn(a0, bf16_to_f32(x.x & 0xffffu));
         a1 = __fadd_rn(a1, bf16_to_f32(x.x >> 16));
         a2 = __fadd_rn(a2, bf16_to_f32(x.y & 0xffffu));
@@ -142,7 +146,7 @@ __device__ __forceinline__ void publish_item(uint2 *p_local, uint2 v, const Peer
     } else {
 #pragma unroll
         for (int r = 0; r < kMaxPeers; ++r)
-            if (r < pa.world) __stcs((uint2 *)((char *)p_local + pa.p_peer[r]), v);
+            if (r < pa.world) st_peer((uint2 *)((char *)p_local + pa.p_peer[r]), v);
     }
 }
 

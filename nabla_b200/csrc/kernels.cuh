@@ -24,10 +24,15 @@ namespace nbo {
 
 // ---- helpers ----------------------------------------------------------------
 
-__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
-__device__ __forceinline__ uint2 ld_stream(const uint2 *p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(uint2 *p, uint2 v) { __stcs(p, v); }
+// Plain (default cache operator) 128-bit / 64-bit accesses.  Measured on B200 against the
+// streaming (.cs), .cg and .lu/.wt operators on every array role (state that is read and
+// rewritten, gradients read once, bf16 parameters written once): the default operator was the
+// fastest or tied in every combination, 2-7 % faster than .cs on both for the update kernels
+// (35.3 vs 37.9 ms on 8 G parameters), so no eviction hint is given anywhere.
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return *p; }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { *p = v; }
+__device__ __forceinline__ uint2 ld_stream(const uint2 *p) { return *p; }
+__device__ __forceinline__ void st_stream(uint2 *p, uint2 v) { *p = v; }
 
 // bf16 -> f32 is a 16-bit shift (half 2.7.1 bf16::to_f32).
 __device__ __forceinline__ float bf16_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
