@@ -11,8 +11,10 @@ all-gather (the collectives vanish at N = 1).  One JSON line is printed by rank 
             max over ranks, K steps after W warm-up steps.
   roofline  the fused update kernel: 28 algorithmic bytes per element over its own launch duration (CUDA
             events recorded by the library around the launch), against the measured copy bandwidth.
-  e2e       the same step through the public API with HOST buffers: gradients copied from pinned host
-            memory and the updated bf16 params of this rank's shard copied back, inside the timed region.
+  e2e       the same step through the public API with HOST buffers, copies inside the timed region: at
+            N = 1 the host-streamed step (gradients in from pinned host memory, update, bf16 params back
+            out, pipelined slice by slice so both PCIe directions run at once); at N > 1 the gradients
+            copied in, the sharded step, and the updated params of this rank's shard copied back.
   cpu_baseline (N = 1, rank 0)  the CPU oracle in the reference's own 12-pass shape on a bounded sample.
 
 `--impl reference` times that CPU port on the host cores alone (rank 0 only).
@@ -328,19 +330,36 @@ def run_ours(args, wl_name, wl):
         ring_in.copy_(gflat[:ring_elems])
         ring_out = torch.empty(min(ring_elems, shard), dtype=torch.bfloat16).pin_memory()
 
-        def e2e_step():
-            for off in range(0, padded, ring_elems):
-                m = min(ring_elems, padded - off)
-                gflat[off:off + m].copy_(ring_in[:m], non_blocking=True)
-            step()
-            ro = ring_out.numel()
-            for off in range(b, e, ro):
-                m = min(ro, e - off)
-                ring_out[:m].copy_(pflat[off:off + m], non_blocking=True)
-            torch.cuda.synchronize()
+        if world == 1:
+            # host tensors (one per parameter tensor, as the reference's CPU tensors are) aliased onto the
+            # two pinned rings; the step streams them through the device buckets slice by slice
+            hp_ptrs, hg_ptrs, off = [], [], 0
+            for n in sizes:
+                if off + n > ring_elems:
+                    off = 0
+                hg_ptrs.append(ring_in.data_ptr() + 2 * off)
+                hp_ptrs.append(ring_out.data_ptr() + 2 * off)
+                off += n
+            hpa, hga = nb._lib.ptr_array(hp_ptrs), nb._lib.ptr_array(hg_ptrs)
+
+            def e2e_step():
+                opt.step_host_ptrs(pp, gp, hpa, hga, use_scaler=False, max_norm=0.0)
+            e2e_path = "nbo_zero1_step_host: copy-in / update / copy-out pipelined over 3 streams, 32 Mi-element slices"
+        else:
+            def e2e_step():
+                for off in range(0, padded, ring_elems):
+                    m = min(ring_elems, padded - off)
+                    gflat[off:off + m].copy_(ring_in[:m], non_blocking=True)
+                step()
+                ro = ring_out.numel()
+                for off in range(b, e, ro):
+                    m = min(ro, e - off)
+                    ring_out[:m].copy_(pflat[off:off + m], non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_path = "copy-in, sharded step, copy-out of the shard, in stream order"
         h2d, d2h = 2 * padded * world, 2 * shard * world
         parallelism = f"zero1-dp{world}"
-        staging = "1 GiB pinned ring reused for every chunk of the step's gradients / updated params"
+        staging = "two 1 GiB pinned rings (gradients in, params out); the host tensors / chunks alias them"
     else:
         mixed = wl["kind"] == "mixed"
         dt = torch.bfloat16 if mixed else torch.float32
@@ -380,11 +399,23 @@ def run_ours(args, wl_name, wl):
         host_g.copy_(flat_g)
         host_p = torch.empty(flat_p.numel(), dtype=dt).pin_memory()
 
-        def e2e_step():
-            flat_g.copy_(host_g, non_blocking=True)
-            step()
-            host_p.copy_(flat_p, non_blocking=True)
-            torch.cuda.synchronize()
+        if mixed:
+            hp_ptrs, hg_ptrs = [], []
+            for t_p, t_g in zip(ps, gs):
+                hp_ptrs.append(host_p.data_ptr() + (t_p.data_ptr() - flat_p.data_ptr()))
+                hg_ptrs.append(host_g.data_ptr() + (t_g.data_ptr() - flat_g.data_ptr()))
+            hpa, hga = nb._lib.ptr_array(hp_ptrs), nb._lib.ptr_array(hg_ptrs)
+
+            def e2e_step():
+                opt.step_host_ptrs(pa, ga, hpa, hga, use_scaler=wl["use_scaler"], max_norm=wl["max_norm"])
+            e2e_path = "nbo_step_mixed_host: copy-in / update / copy-out pipelined over 3 streams, 32 Mi-element slices"
+        else:
+            def e2e_step():
+                flat_g.copy_(host_g, non_blocking=True)
+                step()
+                host_p.copy_(flat_p, non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_path = "copy-in, step, copy-out, in stream order"
         h2d = d2h = flat_g.numel() * es
         parallelism = "single-gpu"
         staging = "whole gradient / param buffers in pinned host memory"
@@ -502,7 +533,7 @@ def run_ours(args, wl_name, wl):
         "kernel_ms": {"update": upd_ms, "norm_nonfinite": norm_ms},
         "step_hbm_gbs_per_gpu": step_bytes / (dev_s / args.steps) / 1e9,
         "e2e": {"value": total / e2e_s, "unit": "params/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "path": e2e_path},
         "gpu_launches": launches,
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                    "samples": clocks["samples"]},

@@ -290,6 +290,26 @@ NBO_API int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *
 NBO_API int32_t nbo_step_mixed_collect(nbo_optimizer *h, nbo_step_result *result,
                                        uint64_t *steps_enqueued);
 
+/* The same step for a caller whose gradients and parameters live in HOST
+ * memory, as every tensor of nabla's CPU backend does (nabla-core/src/cpu/
+ * mod.rs; the optimizer reads `grads[i]` and writes `params[i]` in place,
+ * alg.rs:109-150).  `params_dev` / `grads_dev` are device staging buffers of
+ * the declared sizes (what nbo_step_mixed takes); `params_host` /
+ * `grads_host` hold one host pointer per tensor.  The chunk list is cut into
+ * slices of about `slice_elems` elements (0 = 32 Mi) and pipelined over three
+ * streams - gradients host->device, update, parameters device->host - so both
+ * PCIe directions run at once and the update hides behind them; the fp32
+ * master / m / v state stays in HBM.  With use_scaler or max_norm > 0 every
+ * gradient is copied in first (the decision needs all of them); a skipped
+ * step copies nothing out.  Host buffers should be page-locked, otherwise
+ * the copies do not overlap.  The call returns when the host parameters are
+ * complete.  Same kernels and arithmetic as nbo_step_mixed: results are
+ * bit-identical.  Unsharded mixed-precision handles. */
+NBO_API int32_t nbo_step_mixed_host(nbo_optimizer *h, uint64_t n, void *const *params_dev,
+                                    const void *const *grads_dev, void *const *params_host,
+                                    const void *const *grads_host, uint64_t slice_elems,
+                                    int32_t use_scaler, double max_norm, nbo_step_result *result);
+
 /* ---- LR schedules (pure host math) --------------------------------------- */
 
 /* lr_at_step (nabla-train/src/optim/core.rs:130-173); `step` is the trainer's
@@ -340,6 +360,16 @@ NBO_API int32_t nbo_zero1_init_master(nbo_optimizer *h, const void *params_flat_
 NBO_API int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat_bf16, void *grads_flat_bf16,
                                int32_t average, int32_t use_scaler, double max_norm,
                                nbo_step_result *result);
+
+/* nbo_step_mixed_host for a ZeRO-1 handle of world size 1 (the single-GPU end
+ * of the sharded configuration): device staging is the two flat buckets, the
+ * host side is one pointer per tensor of the declared list (n = that list's
+ * length).  With world > 1 it returns NBO_ERR_STATE: the reduce-scatter needs
+ * every rank's whole bucket on the device before the first update. */
+NBO_API int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, void *grads_flat_dev,
+                                    uint64_t n, void *const *params_host,
+                                    const void *const *grads_host, uint64_t slice_elems,
+                                    int32_t use_scaler, double max_norm, nbo_step_result *result);
 
 /* The same step with the two collectives fused into the kernels over NVLink /
  * NVSwitch peer memory instead of issued as separate NCCL passes.  Both flat

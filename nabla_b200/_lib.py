@@ -87,6 +87,8 @@ SIGNATURES = {
     "nbo_step_mixed": (C.c_int32, [_H, C.c_uint64, _PP, _PP, C.c_int32, C.c_double, C.POINTER(StepResult)]),
     "nbo_step_mixed_async": (C.c_int32, [_H, C.c_uint64, _PP, _PP, C.c_int32, C.c_double]),
     "nbo_step_mixed_collect": (C.c_int32, [_H, C.POINTER(StepResult), _U64P]),
+    "nbo_step_mixed_host": (C.c_int32, [_H, C.c_uint64, _PP, _PP, _PP, _PP, C.c_uint64, C.c_int32, C.c_double,
+                                        C.POINTER(StepResult)]),
     "nbo_lr_at_step": (C.c_int32, [C.POINTER(LrScheduleC), C.c_double, C.c_uint64, _F64P]),
     "nbo_zero1_unique_id": (C.c_int32, [C.c_void_p]),
     "nbo_zero1_geometry": (C.c_int32, [C.c_uint64, C.c_int32, _U64P, _U64P]),
@@ -95,6 +97,8 @@ SIGNATURES = {
     "nbo_zero1_init_master": (C.c_int32, [_H, C.c_void_p]),
     "nbo_zero1_step": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_double,
                                    C.POINTER(StepResult)]),
+    "nbo_zero1_step_host": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_uint64, _PP, _PP, C.c_uint64, C.c_int32,
+                                        C.c_double, C.POINTER(StepResult)]),
     "nbo_zero1_attach_symmetric": (C.c_int32, [_H, C.c_void_p, _PP, C.c_void_p, C.c_void_p, _PP, C.c_void_p,
                                                C.c_int32]),
     "nbo_zero1_step_fused": (C.c_int32, [_H, C.c_int32, C.c_int32, C.c_double, C.POINTER(StepResult)]),

@@ -30,7 +30,8 @@ struct Piece {
     int32_t group;
 };
 
-struct Zero1;  // defined in zero1.cu
+struct Zero1;     // defined in zero1.cu
+struct HostPipe;  // defined in host_step.cu
 
 }  // namespace nbo
 
@@ -92,6 +93,8 @@ struct nbo_optimizer {
 
     nbo::Zero1 *zero1 = nullptr;
     double zero1_timeout_s = 600.0;
+
+    nbo::HostPipe *host_pipe = nullptr;  // copy streams + events of the host-streamed step, made on first use
 };
 
 namespace nbo {
@@ -160,5 +163,29 @@ void commit_step(nbo_optimizer *h, bool checked, bool use_scaler, nbo_step_resul
 int32_t prof_mark(nbo_optimizer *h, int i);
 
 void zero1_destroy(nbo_optimizer *h);
+void host_pipe_destroy(nbo_optimizer *h);
+
+// Host-streamed mixed-precision step over the table as currently bound (host_step.cu).  `host_p` /
+// `host_g` hold one host pointer per caller tensor.
+int32_t host_streamed_step(nbo_optimizer *h, void *const *host_p, const void *const *host_g,
+                           uint64_t slice_elems, int32_t use_scaler, double max_norm, nbo_step_result *result);
+
+// Brings the decision record to the host (synchronises the stream).
+int32_t read_ctrl(nbo_optimizer *h);
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// Every entry point that reads or changes host-side optimizer / scaler state starts with this.
+#define NBO_SYNC_STATE(h)                                               \
+    do {                                                                \
+        if ((h) && (h)->dev_newer) {                                    \
+            int32_t rc__ = nbo::collect_dev_state((nbo_optimizer *)(h)); \
+            if (rc__ != NBO_OK) return rc__;                            \
+        }                                                               \
+    } while (0)
 
 }  // namespace nbo

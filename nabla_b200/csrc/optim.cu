@@ -258,7 +258,7 @@ int32_t prof_mark(nbo_optimizer *h, int i)
     return NBO_OK;
 }
 
-static int32_t read_ctrl(nbo_optimizer *h)
+int32_t read_ctrl(nbo_optimizer *h)
 {
     NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
                                 h->stream));
@@ -280,21 +280,6 @@ int32_t collect_dev_state(nbo_optimizer *h)
     h->dev_newer = false;
     return NBO_OK;
 }
-
-// Every entry point that reads or changes host-side optimizer / scaler state starts with this.
-#define NBO_SYNC_STATE(h)                                          \
-    do {                                                           \
-        if ((h) && (h)->dev_newer) {                               \
-            int32_t rc__ = collect_dev_state((nbo_optimizer *)(h)); \
-            if (rc__ != NBO_OK) return rc__;                       \
-        }                                                          \
-    } while (0)
-
-struct DeviceGuard {
-    int prev = -1;
-    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
-    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
-};
 
 static bool valid_kind(int32_t k) { return k == NBO_ADAMW || k == NBO_ADAM || k == NBO_SGD; }
 
@@ -363,6 +348,7 @@ int32_t nbo_destroy(nbo_optimizer *h)
     DeviceGuard guard(h->device);
     cudaStreamSynchronize(h->stream);
     zero1_destroy(h);
+    host_pipe_destroy(h);
     free_table(h);
     cudaFree(h->d_partial_sum); cudaFree(h->d_partial_bad); cudaFree(h->d_ticket);
     cudaFree(h->d_local); cudaFree(h->d_ctrl);

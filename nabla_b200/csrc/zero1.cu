@@ -358,6 +358,25 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
     return NBO_OK;
 }
 
+int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, void *grads_flat_dev, uint64_t n,
+                            void *const *params_host, const void *const *grads_host, uint64_t slice_elems,
+                            int32_t use_scaler, double max_norm, nbo_step_result *result)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    Zero1 *z = h->zero1;
+    if (z->world != 1)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the host-streamed step is single-rank; with world > 1 "
+                                      "copy the gradient bucket in and call nbo_zero1_step");
+    if (!params_flat_dev || !grads_flat_dev) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
+    if (n != h->ntensors || (n && (!params_host || !grads_host)))
+        return fail(h, NBO_ERR_INVALID, "nabla-train: params/grads length mismatch: " + std::to_string(n) +
+                                            " host tensors for " + std::to_string(h->ntensors));
+    DeviceGuard guard(h->device);
+    int32_t rc = bind_flat(h, params_flat_dev, grads_flat_dev);
+    if (rc != NBO_OK) return rc;
+    return host_streamed_step(h, params_host, grads_host, slice_elems, use_scaler, max_norm, result);
+}
+
 int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local, void *const *grads_peers,
                                    void *grads_mc, void *params_local, void *const *params_peers,
                                    void *params_mc, int32_t transport)

@@ -298,6 +298,21 @@ public:
         detail::check(h(), nbo_step_mixed(h(), p_.size(), p_.data(), g_.data(), use_scaler, max_norm, &r));
         return r;
     }
+    // The same step for bf16 gradients / parameters held in host memory (one pointer per tensor, ideally
+    // page-locked): copied in, updated and copied out slice by slice on three streams.  The device
+    // tensors are staging.
+    nbo_step_result step_host(const std::vector<Tensor *> &params_dev, const std::vector<const Tensor *> &grads_dev,
+                              const std::vector<void *> &params_host, const std::vector<const void *> &grads_host,
+                              bool use_scaler = true, double max_norm = 0.0, uint64_t slice_elems = 0)
+    {
+        if (params_host.size() != params_dev.size() || grads_host.size() != grads_dev.size())
+            throw std::invalid_argument("nabla-train: AdamW params/grads length mismatch");
+        collect_ptrs(params_dev, grads_dev);
+        nbo_step_result r{};
+        detail::check(h(), nbo_step_mixed_host(h(), p_.size(), p_.data(), g_.data(), params_host.data(),
+                                               grads_host.data(), slice_elems, use_scaler, max_norm, &r));
+        return r;
+    }
     // Enqueue only; optimizer and scaler state advance on the device (graph-capturable).
     void step_async(const std::vector<Tensor *> &params_bf16, const std::vector<const Tensor *> &grads_bf16,
                     bool use_scaler = true, double max_norm = 0.0)

@@ -675,6 +675,33 @@ class MixedAdamW:
                                                  1 if use_scaler else 0, float(max_norm), C.byref(res)))
         return StepOutcome.from_c(res)
 
+    def step_host(self, params_dev, grads_dev, params_host, grads_host, *, use_scaler: bool = True,
+                  max_norm: float = 0.0, slice_elems: int = 0) -> StepOutcome:
+        """The same step for gradients and parameters that live in HOST memory (pinned, for overlap):
+        gradients are copied in, updated and the bf16 parameters copied out slice by slice on three
+        streams, so both PCIe directions run at once; `params_dev` / `grads_dev` are device staging
+        tensors of the same shapes.  Returns when `params_host` is complete."""
+        n = len(self._numel)
+        assert len(params_dev) == len(grads_dev) == len(params_host) == len(grads_host) == n, \
+            "nabla-train: AdamW params/grads length mismatch"
+        _check_tensors(params_dev, torch.bfloat16, "params")
+        _check_tensors(grads_dev, self._grad_dtype, "grads")
+        for i, (p, g) in enumerate(zip(params_host, grads_host)):
+            if p.is_cuda or g.is_cuda or p.dtype != torch.bfloat16 or g.dtype != self._grad_dtype \
+                    or not p.is_contiguous() or not g.is_contiguous() \
+                    or p.numel() != self._numel[i] or g.numel() != self._numel[i]:
+                raise ValueError(f"host tensor {i}: expected contiguous CPU tensors of {self._numel[i]} elements")
+        return self.step_host_ptrs(_ptrs(params_dev), _ptrs(grads_dev), _ptrs(params_host), _ptrs(grads_host),
+                                   use_scaler=use_scaler, max_norm=max_norm, slice_elems=slice_elems)
+
+    def step_host_ptrs(self, params_dev_arr, grads_dev_arr, params_host_arr, grads_host_arr, *,
+                       use_scaler=True, max_norm=0.0, slice_elems=0) -> StepOutcome:
+        res = L.StepResult()
+        self._h.check(self._h.lib.nbo_step_mixed_host(
+            self._h.h, len(self._numel), params_dev_arr, grads_dev_arr, params_host_arr, grads_host_arr,
+            int(slice_elems), 1 if use_scaler else 0, float(max_norm), C.byref(res)))
+        return StepOutcome.from_c(res)
+
     def step_async(self, params_arr, grads_arr, *, use_scaler=True, max_norm=0.0) -> None:
         """Enqueues one step and returns without waiting; the step counter, bias corrections and loss-scale
         bookkeeping advance on the device.  Every launch has constant arguments, so the call can be captured

@@ -121,6 +121,16 @@ class Zero1AdamW:
                                                  float(max_norm), C.byref(res)))
         return StepOutcome.from_c(res)
 
+    def step_host_ptrs(self, params_ptr: int, grads_ptr: int, params_host_arr, grads_host_arr, *,
+                       use_scaler=False, max_norm=0.0, slice_elems=0) -> StepOutcome:
+        """World size 1 only: gradients come from, and parameters return to, HOST tensors (one pointer per
+        declared tensor, `_lib.ptr_array`), pipelined slice by slice through the two flat device buckets."""
+        res = L.StepResult()
+        self._h.check(self._h.lib.nbo_zero1_step_host(
+            self._h.h, C.c_void_p(params_ptr), C.c_void_p(grads_ptr), len(params_host_arr), params_host_arr,
+            grads_host_arr, int(slice_elems), 1 if use_scaler else 0, float(max_norm), C.byref(res)))
+        return StepOutcome.from_c(res)
+
     # ---- fused path over NVLink / NVSwitch peer memory -------------------------------------------
     def attach_symmetric(self, group=None, transport: int = 0):
         """Allocates the two flat bf16 buckets in symmetric memory (torch.distributed._symmetric_memory:

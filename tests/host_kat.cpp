@@ -116,6 +116,12 @@ int main()
         r = opt.collect(&done);
         REQUIRE(done == 1 && r.applied == 0 && r.loss_scale == 16384.0 && opt.step_count() == 1);
         REQUIRE(std::fabs(opt.master(0)[5] - 0.9f) < 1e-6f);
+        // host-streamed step from ordinary (pageable) host vectors, 1-chunk slices: a finite gradient moves
+        // every parameter by lr again; the result lands in the host vector, not only in the staging tensor
+        std::vector<uint16_t> host_g(n, bf16(0.5f * 16384.0f)), host_p(n, 0);
+        r = opt.step_host({&p}, {&g}, {host_p.data()}, {host_g.data()}, true, 0.0, 4096);
+        REQUIRE(r.applied == 1 && r.step_count == 2 && r.loss_scale == 16384.0);
+        REQUIRE(std::fabs(unbf16(host_p[0]) - 0.8f) < 4e-3f && host_p[0] == host_p[n - 1] && host_p[0] == host_p[4096]);
     }
     std::printf("HOST_KAT_OK\n");
     return 0;
