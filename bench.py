@@ -174,9 +174,11 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU arm (oracle port)
 
-def cpu_reference_step_time(sample_elems, steps, warmup, mixed=True):
+def cpu_reference_step_time(sample_elems, steps, warmup, mixed=True, passes=True):
     """Times the reference-shaped CPU port (12-pass AdamW incl. the serial `map`, plus - for the mixed step -
-    the serial cast / scaler / clip walks) on `sample_elems` elements.  Returns (seconds per step, cores)."""
+    the serial cast / scaler / clip walks) on `sample_elems` elements.  `passes=False` times the port's
+    single fused pass over the same data instead (context only: nabla's CPU backend does not run that).
+    Returns (seconds per step, cores)."""
     import numpy as np
     from oracle import binding as orc
     orc.build()
@@ -188,14 +190,14 @@ def cpu_reference_step_time(sample_elems, steps, warmup, mixed=True):
     if mixed:
         mo = orc.MixedOracle([w], [orc.AdamCfg(3e-4, 0.9, 0.999, 1e-8, 0.1, 1)], use_scaler=False)
         g16 = orc.bf16_from_f32(g)
-        fn = lambda: mo.step([g16], max_norm=0.0, passes=True)
+        fn = lambda: mo.step([g16], max_norm=0.0, passes=passes)
     else:
         m = np.zeros(n, np.float32); v = np.zeros(n, np.float32)
         st = [0]
 
         def fn():
             st[0] += 1
-            orc.adam_step(w, g, m, v, 1e-3, step=st[0], decoupled=False, passes=True)
+            orc.adam_step(w, g, m, v, 1e-3, step=st[0], decoupled=False, passes=passes)
     for _ in range(warmup):
         fn()
     t0 = time.perf_counter()
@@ -554,9 +556,12 @@ def run_ours(args, wl_name, wl):
         mixed = wl["kind"] != "f32"
         sample = min(calibrated_cpu_sample(12.0, mixed), total)
         sec, cores = cpu_reference_step_time(sample, 1, 0, mixed)
+        fused_sec, _ = cpu_reference_step_time(sample, 1, 0, mixed, passes=False)
         line["cpu_baseline"] = {"value": sample / sec, "unit": "params/s", "cores": cores, "kind": "port",
                                 "sample": f"1 step on {sample} elements ({sec:.1f} s), reference-shaped 12-pass "
-                                          "AdamW incl. the serial map / cast walks"}
+                                          "AdamW incl. the serial map / cast walks",
+                                "fused_single_pass_value": sample / fused_sec,
+                                "fused_note": "the same port as one fused pass (context; not what the reference runs)"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
