@@ -104,13 +104,15 @@ def test_rank_that_never_arrives_times_out(nb):
     assert abs(float(p[0]) - 0.9) < 1e-6
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer"])
-def test_rank_leaving_between_steps_ends_in_a_timeout(mode):
+def test_rank_leaving_between_steps_ends_in_a_timeout():
+    """Only the NCCL path is exercised: its buckets are ordinary device memory and NVLS is off, so the
+    rank that leaves holds no NVLink multicast binding.  Symmetric-memory buckets (the fused path) are
+    always bound to a multicast object where the fabric offers one, and a rank must not end in that state."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", str(29580 + (mode == "peer")),
-           os.path.join(ROOT, "tests", "zero1_leave_worker.py"), mode]
+           "--master-addr", "127.0.0.1", "--master-port", "29580",
+           os.path.join(ROOT, "tests", "zero1_leave_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert "ZERO1_LEAVE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

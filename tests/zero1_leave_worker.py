@@ -1,9 +1,8 @@
 """Failure detection of the sharded step, made on the host: after two good steps rank 1 leaves between steps
 (nothing of its own in flight); rank 0's next step must end with NBO_ERR_TIMEOUT within the configured limit,
 leave the CUDA context usable, and refuse further sharded steps.  Launched by tests/test_gpu_zero1.py on two
-GPUs with NVLS off; the fused variant uses plain peer loads/stores only.
-
-    zero1_leave_worker.py [nccl|peer]
+GPUs with NVLS off.  The buckets are ordinary device memory and the collectives go through NCCL, so no
+NVLink multicast object is bound anywhere when the rank leaves (symmetric-memory buckets would be).
 """
 import os
 import sys
@@ -18,7 +17,6 @@ import nabla_b200 as nb  # noqa: E402
 
 
 def main():
-    mode = sys.argv[1] if len(sys.argv) > 1 else "nccl"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
@@ -26,13 +24,10 @@ def main():
     total = sum(sizes)
     z = nb.Zero1AdamW.adamw(3e-4, 0.1, [(n,) for n in sizes], rank, world, nb.exchange_unique_id(rank, world),
                             timeout_s=4.0)
-    if mode == "nccl":
-        pflat = torch.zeros(z.padded, dtype=torch.bfloat16, device="cuda")
-        gflat = torch.zeros(z.padded, dtype=torch.bfloat16, device="cuda")
-        step = lambda: z.step(pflat, gflat, average=True)
-    else:
-        pflat, gflat = z.attach_symmetric(transport=1)
-        step = lambda: z.step_fused(average=True)
+    assert os.environ.get("NCCL_NVLS_ENABLE") == "0", "run this worker with NCCL_NVLS_ENABLE=0"
+    pflat = torch.zeros(z.padded, dtype=torch.bfloat16, device="cuda")
+    gflat = torch.zeros(z.padded, dtype=torch.bfloat16, device="cuda")
+    step = lambda: z.step(pflat, gflat, average=True)
     pflat[:total] = 0.01
     gflat[:total] = 1e-4
     z.init_master(pflat)
@@ -63,7 +58,7 @@ def main():
     nb.Sgd(0.1, [(1000,)]).step([p], [torch.ones(1000, device="cuda")])
     torch.cuda.synchronize()
     assert abs(float(p[0]) - 0.9) < 1e-6
-    print("ZERO1_LEAVE_OK", mode, f"{dt:.1f}s", flush=True)
+    print("ZERO1_LEAVE_OK", f"{dt:.1f}s", flush=True)
     os._exit(0)                           # the torch process group cannot be torn down without its peer
 
 
