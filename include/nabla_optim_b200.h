@@ -171,7 +171,9 @@ NBO_API int32_t nbo_set_lr(nbo_optimizer *h, double lr);
 NBO_API int32_t nbo_get_lr(const nbo_optimizer *h, int32_t group_id, double *lr);
 
 /* zero_grad (nabla-ml/src/autograd/ops.rs:1668-1673): every gradient of the
- * bound list becomes zeros (memset on the stream).  `elem_size` 4 or 2. */
+ * bound list becomes +0 (one kernel over the table on the stream).  The element
+ * size follows the handle's precision: bf16 gradients for NBO_MIXED_BF16, fp32
+ * otherwise. */
 NBO_API int32_t nbo_zero_grad(nbo_optimizer *h, uint64_t n, void *const *grads);
 
 /* Gradient accumulation, accum[i] = accum[i] + grads[i] elementwise in fp32
@@ -244,8 +246,10 @@ NBO_API int32_t nbo_grad_norm(nbo_optimizer *h, uint64_t n, const void *const *g
  *             out_dev[0] = sum of squares (the norm is its sqrt),
  *             out_dev[1] = 1.0 if any element is inf/NaN else 0.0
  * Asynchronous on `stream`.  The first call on a device looks up the device
- * address of the scratch array (cudaGetSymbolAddress) and should therefore be
- * made before any stream capture begins.  Every call shares the one scratch
+ * address of the scratch array (cudaGetSymbolAddress) and has the driver load
+ * the kernels of both precisions, and should therefore be made - once per
+ * device, either precision - before any stream capture begins and before the
+ * caller's memory budget is fixed.  Every call shares the one scratch
  * array: calls that may overlap on the GPU (different streams without an
  * ordering between them) race on it and must be serialised by the caller. */
 NBO_API int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const void *grads, uint64_t n,

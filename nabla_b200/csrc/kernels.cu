@@ -354,7 +354,7 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
 {
     using namespace nbo;
     static NoAllocScratch *scratch_of[64] = {nullptr};  // device address of the array, per device
-    static int sms_of[64] = {0};
+    static int grid_of[64][2] = {{0}};                  // persistent grid per device: [fp32, bf16]
     if (device < 0 || device >= 64)
         return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_grad_norm_noalloc: device index out of range");
     if (!out_dev || (n && !grads))
@@ -381,7 +381,22 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
             // The array's name is only a host-side stand-in: ask the runtime for its address on THIS device.
             void *p = nullptr;
             NBO_CUDA(nullptr, cudaGetSymbolAddress(&p, g_noalloc_scratch));
-            NBO_CUDA(nullptr, cudaDeviceGetAttribute(&sms_of[device], cudaDevAttrMultiProcessorCount, device));
+            int sms = 0;
+            NBO_CUDA(nullptr, cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+            // Touch every kernel this entry point can launch, for both precisions, so that the driver loads
+            // their code now (with lazy module loading a kernel's first use makes the driver set aside device
+            // memory for it) and one warm-up call per device covers fp32 and bf16 alike.
+            cudaFuncAttributes fa;
+            NBO_CUDA(nullptr, cudaFuncGetAttributes(&fa, (const void *)noalloc_setup_kernel));
+            const void *ks[2] = {(const void *)norm_kernel<false, true>, (const void *)norm_kernel<true, true>};
+            for (int b = 0; b < 2; ++b) {
+                NBO_CUDA(nullptr, cudaFuncGetAttributes(&fa, ks[b]));
+                int per_sm = 0;
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ks[b], kBlock, 0) != cudaSuccess || per_sm < 1)
+                    per_sm = 1;
+                long long g = (long long)sms * per_sm;
+                grid_of[device][b] = (int)(g > kNoAllocMaxGrid ? kNoAllocMaxGrid : g);
+            }
             scratch_of[device] = static_cast<NoAllocScratch *>(p);
         }
         NoAllocScratch *s = scratch_of[device];
@@ -392,12 +407,7 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
         uint32_t setup_blocks = nchunks / 256 + 1;
         noalloc_setup_kernel<<<setup_blocks, 256, 0, st>>>(grads, n, head, nchunks);
         NBO_CUDA(nullptr, cudaGetLastError());
-        int per_sm = 0;
-        const void *k = bf16 ? (const void *)norm_kernel<true, true> : (const void *)norm_kernel<false, true>;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kBlock, 0) != cudaSuccess || per_sm < 1)
-            per_sm = 1;
-        long long grid = (long long)sms_of[device] * per_sm;
-        if (grid > kNoAllocMaxGrid) grid = kNoAllocMaxGrid;
+        long long grid = grid_of[device][bf16 ? 1 : 0];
         long long units = ((long long)nchunks + kNormBatch - 1) / kNormBatch;
         if (grid > units) grid = units;
         if (grid < 1) grid = 1;

@@ -148,6 +148,48 @@ __device__ __forceinline__ ChunkView chunk_view(const TensorDesc &d, const Chunk
 
 // ---- fp32 Adam / AdamW --------------------------------------------------------
 
+// One chunk of fp32 Adam / AdamW: 16 independent 128-bit loads per thread go out before the first result
+// is needed.  Shared by the table-driven kernel and the single-tensor one below.
+__device__ __forceinline__ void adam_f32_chunk(const TensorDesc &d, const ChunkView &cv, const AdamHP &hp)
+{
+    float *P = (float *)d.p;
+    const float *G = (const float *)d.g;
+    float4 *p4 = (float4 *)(P + cv.item0);
+    const float4 *g4 = (const float4 *)(G + cv.item0);
+    float4 *m4 = (float4 *)(d.s0 + cv.item0);
+    float4 *v4 = (float4 *)(d.s1 + cv.item0);
+
+    float4 p[kItemsPerThread], g[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+#pragma unroll
+    for (int u = 0; u < kItemsPerThread; ++u) {
+        uint32_t i = threadIdx.x + u * kBlock;
+        if (i < cv.nitems) {
+            g[u] = ld_stream(g4 + i);
+            p[u] = ld_stream(p4 + i);
+            m[u] = ld_stream(m4 + i);
+            v[u] = ld_stream(v4 + i);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kItemsPerThread; ++u) {
+        uint32_t i = threadIdx.x + u * kBlock;
+        if (i < cv.nitems) {
+            adam_elem(p[u].x, g[u].x, m[u].x, v[u].x, hp);
+            adam_elem(p[u].y, g[u].y, m[u].y, v[u].y, hp);
+            adam_elem(p[u].z, g[u].z, m[u].z, v[u].z, hp);
+            adam_elem(p[u].w, g[u].w, m[u].w, v[u].w, hp);
+            st_stream(p4 + i, p[u]);
+            st_stream(m4 + i, m[u]);
+            st_stream(v4 + i, v[u]);
+        }
+    }
+    // head / tail / unaligned elements
+    for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock)
+        adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
+    for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock)
+        adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
+}
+
 __global__ void __launch_bounds__(kBlock)
 adam_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
                 uint32_t nchunks, AdamHP hp)
@@ -155,43 +197,7 @@ adam_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ 
     for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck);
-        float *P = (float *)d.p;
-        const float *G = (const float *)d.g;
-        float4 *p4 = (float4 *)(P + cv.item0);
-        const float4 *g4 = (const float4 *)(G + cv.item0);
-        float4 *m4 = (float4 *)(d.s0 + cv.item0);
-        float4 *v4 = (float4 *)(d.s1 + cv.item0);
-
-        float4 p[kItemsPerThread], g[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                g[u] = ld_stream(g4 + i);
-                p[u] = ld_stream(p4 + i);
-                m[u] = ld_stream(m4 + i);
-                v[u] = ld_stream(v4 + i);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                adam_elem(p[u].x, g[u].x, m[u].x, v[u].x, hp);
-                adam_elem(p[u].y, g[u].y, m[u].y, v[u].y, hp);
-                adam_elem(p[u].z, g[u].z, m[u].z, v[u].z, hp);
-                adam_elem(p[u].w, g[u].w, m[u].w, v[u].w, hp);
-                st_stream(p4 + i, p[u]);
-                st_stream(m4 + i, m[u]);
-                st_stream(v4 + i, v[u]);
-            }
-        }
-        // head / tail / unaligned elements
-        for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock)
-            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
-        for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock)
-            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
+        adam_f32_chunk(d, chunk_view(d, ck), hp);
     }
 }
 
@@ -200,39 +206,8 @@ adam_f32_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ 
 __global__ void __launch_bounds__(kBlock)
 adam_f32_single_kernel(TensorDesc d, uint32_t nchunks, AdamHP hp)
 {
-    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const ChunkView cv = chunk_view(d, c);
-        float *P = (float *)d.p;
-        const float *G = (const float *)d.g;
-        float4 *p4 = (float4 *)(P + cv.item0);
-        const float4 *g4 = (const float4 *)(G + cv.item0);
-        float4 *m4 = (float4 *)(d.s0 + cv.item0);
-        float4 *v4 = (float4 *)(d.s1 + cv.item0);
-        float4 p[kItemsPerThread], g[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                g[u] = ld_stream(g4 + i); p[u] = ld_stream(p4 + i);
-                m[u] = ld_stream(m4 + i); v[u] = ld_stream(v4 + i);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kItemsPerThread; ++u) {
-            uint32_t i = threadIdx.x + u * kBlock;
-            if (i < cv.nitems) {
-                adam_elem(p[u].x, g[u].x, m[u].x, v[u].x, hp);
-                adam_elem(p[u].y, g[u].y, m[u].y, v[u].y, hp);
-                adam_elem(p[u].z, g[u].z, m[u].z, v[u].z, hp);
-                adam_elem(p[u].w, g[u].w, m[u].w, v[u].w, hp);
-                st_stream(p4 + i, p[u]); st_stream(m4 + i, m[u]); st_stream(v4 + i, v[u]);
-            }
-        }
-        for (uint64_t i = cv.s_lo0 + threadIdx.x; i < cv.s_lo1; i += kBlock)
-            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
-        for (uint64_t i = cv.s_hi0 + threadIdx.x; i < cv.s_hi1; i += kBlock)
-            adam_elem(P[i], G[i], d.s0[i], d.s1[i], hp);
-    }
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x)
+        adam_f32_chunk(d, chunk_view(d, c), hp);
 }
 
 // ---- fp32 SGD (plain, weight decay, momentum) --------------------------------

@@ -435,14 +435,17 @@ int32_t nbo_step(nbo_optimizer *h, uint64_t n, void *const *params, const void *
     prof_mark(h, 2);
     for (Group &g : h->groups) {
         uint32_t nc = g.chunk_end - g.chunk_begin;
-        if (g.cfg.kind != NBO_SGD) g.step_count += 1;  // counts even when the group is empty
         if (nc == 0) continue;
         if (g.cfg.kind == NBO_SGD)
             rc = launch_sgd_f32(h, g.chunk_begin, nc, sgd_hparams(g.cfg));
         else
-            rc = launch_adam_f32(h, g.chunk_begin, nc, adam_hparams(g.cfg, g.step_count, 1.0f));
+            rc = launch_adam_f32(h, g.chunk_begin, nc, adam_hparams(g.cfg, g.step_count + 1, 1.0f));
         if (rc != NBO_OK) return rc;
     }
+    // the counters advance only once every group has been launched, so a failed launch leaves them
+    // in step with the state; an empty group counts too (alg.rs:120-121)
+    for (Group &g : h->groups)
+        if (g.cfg.kind != NBO_SGD) g.step_count += 1;
     return prof_mark(h, 3);
 }
 

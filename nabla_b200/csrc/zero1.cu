@@ -5,8 +5,11 @@
 // all-gather over NVLink.
 //
 // NCCL is opened with dlopen on first use, so a single-GPU consumer does not
-// need the library at all; world == 1 never touches it.  Kernels read local
-// memory only: remote data always arrives through an NCCL collective first.
+// need the library at all; world == 1 never touches it.  Two forms of the step
+// live here: nbo_zero1_step, whose kernels read local memory only (remote data
+// arrives through NCCL collectives first), and nbo_zero1_step_fused, whose
+// kernels (fused_nvlink.cuh) load and store the other ranks' buckets directly
+// over NVLink with NCCL used only for the stream-ordered barriers around them.
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>

@@ -71,6 +71,34 @@ def test_non_finite_flag_and_scale(nb):
     assert abs(b - 0.5 * a) <= 1e-12 * a
 
 
+def test_device_free_memory_is_unchanged_across_calls(nb):
+    """The property in the name: after one warm-up call on the device (which looks up the scratch address and
+    has the driver load the kernels of both precisions), calls in either precision leave the amount of
+    free device memory exactly as it was - nothing is allocated, by the library or by the driver for it."""
+    lib = nb._lib.load()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g32 = torch.randn(1 << 20, device="cuda")
+    g16 = torch.randn(1 << 20, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(2, dtype=torch.float64, device="cuda")
+    dev = g32.device.index
+
+    def call(g, prec):
+        rc = lib.nbo_grad_norm_noalloc(dev, stream, C.c_void_p(g.data_ptr()), g.numel(), prec, C.c_float(1.0),
+                                       C.c_void_p(out.data_ptr()))
+        nb._lib.check(None, rc)
+
+    call(g32, nb._lib.NBO_F32)                       # the one warm-up call, fp32 only
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        call(g16, nb._lib.NBO_MIXED_BF16)            # first bf16 call comes after the measurement started
+        call(g32, nb._lib.NBO_F32)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    want = float(torch.linalg.vector_norm(g32.double()))
+    assert abs(float(out[0]) ** 0.5 - want) <= 1e-12 * want
+
+
 def test_unaligned_buffer(nb):
     for dtype, off in ((torch.float32, 1), (torch.float32, 3), (torch.bfloat16, 1), (torch.bfloat16, 3)):
         base = torch.randn(20000, device="cuda").to(dtype)

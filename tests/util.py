@@ -26,13 +26,18 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
     return t.detach().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-def assert_close_rel(got, want, what="", rel=REL_TOL, floor=0.1):
+LAST_WORST = {}  # the most recent assert_close_rel call: {what, floored, unfloored} worst relative errors
+
+
+def assert_close_rel(got, want, what="", rel=REL_TOL, floor=0.1, unfloored_from=1e-3):
     """Elementwise |got - want| <= rel * max(|want|, floor * rms(want)).
 
     The bar is 1e-5 relative.  A purely elementwise relative test is undefined for the handful of
     elements that happen to sit next to zero (a parameter crossing zero has |want| ~ 1e-7 while its
     rounding noise is a few ulp of the update, ~1e-9), so below a tenth of the tensor's RMS the error is
-    measured against that floor instead of against |want|.  Returns the worst relative error seen."""
+    measured against that floor instead of against |want|.  In addition the plain, un-floored
+    |got - want| / |want| is asserted on every element with |want| >= unfloored_from * rms.  Returns the
+    worst (floored) relative error seen; LAST_WORST keeps both figures."""
     got = host(got) if isinstance(got, torch.Tensor) else got
     g, w = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
     assert g.shape == w.shape, what
@@ -51,6 +56,17 @@ def assert_close_rel(got, want, what="", rel=REL_TOL, floor=0.1):
     bad = r > rel
     assert not bad.any(), (f"{what}: {bad.sum()} of {g.size} elements off by more than {rel} relative; "
                            f"worst {r.max():.3e} (abs {err[r.argmax()]:.3e} at value {w[r.argmax()]:.6e})")
+    # The bar as literally worded - |got - want| / |want| with no floor - on every element that is not
+    # vanishingly small next to its tensor (|want| >= 1e-3 * rms): asserted too, and kept for reporting.
+    rms = np.sqrt(np.mean(w * w))
+    sel = np.abs(w) >= unfloored_from * rms
+    worst_plain = 0.0
+    if sel.any() and rms > 0.0:
+        plain = np.where(same[sel], 0.0, err[sel] / np.abs(w[sel]))
+        worst_plain = float(plain.max())
+        assert worst_plain <= rel, (f"{what}: un-floored relative error {worst_plain:.3e} > {rel} on an element "
+                                    f"with |want| >= {unfloored_from} * rms")
+    LAST_WORST.update(what=what, floored=float(r.max()), unfloored=worst_plain)
     return float(r.max())
 
 
