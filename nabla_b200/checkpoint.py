@@ -10,9 +10,12 @@ nabla-ml/src/module/core.rs:66-133:
     params.nbla   same container (written only when named params are passed)
 
 State tensors keep the reference's names: m{i} / v{i} (Adam, AdamW), v{i} (the SGD velocity), prefixed
-g{k}. inside a GroupOptimizer (alg.rs:476-485,620-640; groups.rs:320-328).  The mixed-precision and ZeRO-1
-optimizers additionally store their fp32 masters as w{i}; the reference's loaders skip names that start
-with neither m nor v, so such a file still loads there.
+g{k}. inside a GroupOptimizer (alg.rs:476-485,620-640; groups.rs:320-328), and the reference's shapes:
+every m / v / w tensor is written with its parameter's (rows, cols), because the reference installs a loaded
+tensor as it is (alg.rs:487-518) and its next axpy_inplace insists on equal shapes
+(nabla-core/src/common/tensor/ops.rs:638-646).  On load either layout of the right element count is taken.
+The mixed-precision and ZeRO-1 optimizers additionally store their fp32 masters as w{i}; the reference's
+loaders skip names that start with neither m nor v, so such a file still loads there.
 Numbers in meta.txt are written the way Rust's `{}` prints an f64 (shortest round-trip digits, positional,
 no exponent, no trailing ".0") so files are byte-compatible, and parsed leniently like `str::parse::<f64>`.
 """
@@ -28,7 +31,7 @@ import numpy as np
 import torch
 
 from . import _lib as L
-from .optim import GroupOptimizer, LrSchedule, MixedAdamW
+from .optim import GroupOptimizer, LrSchedule, MixedAdamW, _as_state, _flat_state
 
 NBLA_MAGIC = b"NBLA"
 META_FILE, PARAMS_FILE, OPTIM_FILE = "meta.txt", "params.nbla", "optim.nbla"
@@ -78,6 +81,10 @@ def save_tensors(tensors: Sequence[Tuple[str, np.ndarray]], path: str) -> None:
                 a = a.reshape(1, -1) if a.size else a.reshape(0, 0)
             if a.ndim != 2:
                 a = a.reshape(a.shape[0], -1)
+            if a.shape[0] > 0xFFFFFFFF or a.shape[1] > 0xFFFFFFFF:
+                # the reference writes `rows as u32`, `cols as u32` (module/core.rs:76-78): a larger extent
+                # would wrap silently and the file could not be read back, so it is refused instead
+                raise ValueError(f"tensor {name}: shape {a.shape} does not fit the u32 rows/cols of the nabla format")
             nb = name.encode("utf-8")
             f.write(struct.pack("<I", len(nb)))
             f.write(nb)
@@ -238,14 +245,15 @@ def state_tensors(opt) -> List[Tuple[str, torch.Tensor]]:
             idx = [i for i, g in enumerate(opt._gid_of) if g == gi]
             for which, p in ((0, "m"), (1, "v"), (2, "w")):
                 for li, i in enumerate(idx):
-                    out.append((f"g{gi}.{p}{li}", opt._h.state_export(i, which, opt._numel[i])))
+                    out.append((f"g{gi}.{p}{li}", _as_state(opt._h.state_export(i, which, opt._numel[i]),
+                                                            opt._shapes[i])))
         return out
     return opt.state_tensors()
 
 
 def load_state_tensors(opt, tensors: Sequence[Tuple[str, np.ndarray]]) -> None:
     from .zero1 import Zero1AdamW
-    tens = [(n, torch.from_numpy(np.asarray(a, dtype=np.float32).reshape(-1))) for n, a in tensors]
+    tens = [(n, torch.from_numpy(np.asarray(a, dtype=np.float32))) for n, a in tensors]
     if isinstance(opt, Zero1AdamW):
         opt.load_state_tensors(tens)
         return
@@ -276,7 +284,7 @@ def load_state_tensors(opt, tensors: Sequence[Tuple[str, np.ndarray]]) -> None:
                 for li, i in enumerate(idx):
                     if (gi, p, li) not in slots:
                         raise ValueError(f"missing {p}{li}")
-                    opt._h.state_import(i, which, slots[(gi, p, li)])
+                    opt._h.state_import(i, which, _flat_state(slots[(gi, p, li)], opt._numel[i], f"g{gi}.{p}{li}"))
         return
     opt.load_state_tensors(tens)
 

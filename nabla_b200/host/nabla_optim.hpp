@@ -110,9 +110,13 @@ public:
         detail::check(h(), nbo_state_export(h(), tensor, which, out.data()));
         return out;
     }
+    // (rows, cols) of tensor i's state: the parameter's own shape, which is what the reference writes into a
+    // checkpoint for m{i} / v{i} and what its next axpy_inplace expects after a load
+    // (nabla-ml/src/module/core.rs:76-78; nabla-core/src/common/tensor/ops.rs:638-646)
+    std::pair<size_t, size_t> state_shape(size_t tensor) const { return shapes_.at(tensor); }
     void load_state(size_t tensor, int which, const std::vector<float> &v)
     {
-        if (v.size() != numel_.at(tensor)) throw std::runtime_error("bad tensor key: size mismatch");
+        if (v.size() != numel_.at(tensor)) throw std::runtime_error("nabla: axpy_inplace shapes must match");
         detail::check(h(), nbo_state_import(h(), tensor, which, v.data()));
     }
 
@@ -124,7 +128,7 @@ protected:
     nbo_optimizer *h() const { return handle_->h; }
     void configure_single(const nbo_group_config &cfg, const std::vector<std::pair<size_t, size_t>> &shapes)
     {
-        for (auto &s : shapes) numel_.push_back((uint64_t)s.first * s.second);
+        for (auto &s : shapes) { numel_.push_back((uint64_t)s.first * s.second); shapes_.push_back(s); }
         detail::check(h(), nbo_add_group(h(), &cfg, nullptr));
         detail::check(h(), nbo_set_tensors(h(), numel_.size(), numel_.data(), nullptr, NBO_F32));
     }
@@ -139,6 +143,7 @@ protected:
     std::string name_;
     std::shared_ptr<detail::Handle> handle_;
     std::vector<uint64_t> numel_;
+    std::vector<std::pair<size_t, size_t>> shapes_;
 };
 
 using Shapes = std::vector<std::pair<size_t, size_t>>;
@@ -259,7 +264,7 @@ public:
         };
         for (size_t g = 0; g < groups.size(); ++g) add(groups[g], buckets[g]);
         if (default_group) add(*default_group, def);
-        for (auto &nt : named) numel_.push_back(nt.second->numel());
+        for (auto &nt : named) { numel_.push_back(nt.second->numel()); shapes_.push_back(nt.second->shape()); }
         detail::check(h(), nbo_set_tensors(h(), numel_.size(), numel_.data(), gid.data(), NBO_F32));
     }
     size_t groups() const { return ngroups_; }

@@ -36,6 +36,40 @@ def _numel_of(shape) -> int:
     return n
 
 
+def _shape2d_of(shape) -> Tuple[int, int]:
+    """The (rows, cols) a nabla tensor of this shape has: every reference tensor is 2-D row-major
+    (`param_shapes: &[(usize, usize)]`, alg.rs:20-27).  A bare count or a 1-D shape is one row;
+    more than two dimensions keep the first as rows."""
+    if isinstance(shape, int):
+        return (1, shape)
+    dims = [int(d) for d in shape]
+    if len(dims) == 0:
+        return (1, 1)
+    if len(dims) == 1:
+        return (1, dims[0])
+    cols = 1
+    for d in dims[1:]:
+        cols *= d
+    return (dims[0], cols)
+
+
+def _as_state(flat: torch.Tensor, shape2d: Tuple[int, int]) -> torch.Tensor:
+    """A state tensor as the reference holds it: the parameter's own (rows, cols)."""
+    return flat.reshape(shape2d)
+
+
+def _flat_state(t, numel: int, key: str) -> torch.Tensor:
+    """A loaded state tensor as the flat fp32 run the library stores.  Either layout of the same elements
+    is accepted ((rows, cols) as the reference writes it, or one row); a different element count is what
+    the reference would trip over on its next step (`axpy_inplace ... shapes must match`,
+    nabla-core/src/common/tensor/ops.rs:638-646) and is refused here, before anything is copied."""
+    t = torch.as_tensor(t)
+    if t.numel() != numel:
+        raise ValueError(f"nabla: axpy_inplace shapes must match ({key}: {tuple(t.shape)} holds {t.numel()} "
+                         f"elements, the parameter has {numel})")
+    return t.reshape(-1)
+
+
 def _check_tensors(ts: Sequence[torch.Tensor], dtype, what: str):
     for i, t in enumerate(ts):
         if not t.is_cuda:
@@ -178,12 +212,16 @@ class Optimizer:
         self._h.check(self._h.lib.nbo_zero_grad(self._h.h, len(grads), _ptrs(grads)))
 
     # OptimState (core.rs:64-79): state tensors are named m{i} / v{i}
+    def _state(self, i: int, which: int) -> torch.Tensor:
+        return _as_state(self._h.state_export(i, which, self._numel[i]), self._shapes[i])
+
     def state_tensors(self) -> List[Tuple[str, torch.Tensor]]:
+        """Named m{i} / v{i}, each with its parameter's (rows, cols) as in the reference (alg.rs:476-485)."""
         out = []
-        for i, n in enumerate(self._numel):
-            out.append((f"m{i}", self._h.state_export(i, 0, n)))
-        for i, n in enumerate(self._numel):
-            out.append((f"v{i}", self._h.state_export(i, 1, n)))
+        for i in range(len(self._numel)):
+            out.append((f"m{i}", self._state(i, 0)))
+        for i in range(len(self._numel)):
+            out.append((f"v{i}", self._state(i, 1)))
         return out
 
     def load_state_tensors(self, tensors: Sequence[Tuple[str, torch.Tensor]]) -> None:
@@ -206,9 +244,10 @@ class Optimizer:
         for i, t in enumerate(v):
             if t is None:
                 raise ValueError(f"missing v{i}")
-        for i in range(len(self._numel)):
-            self._h.state_import(i, 0, m[i].reshape(-1))
-            self._h.state_import(i, 1, v[i].reshape(-1))
+        flat = [(_flat_state(m[i], n, f"m{i}"), _flat_state(v[i], n, f"v{i}")) for i, n in enumerate(self._numel)]
+        for i, (mi, vi) in enumerate(flat):
+            self._h.state_import(i, 0, mi)
+            self._h.state_import(i, 1, vi)
 
 
 class _Single(Optimizer):
@@ -216,6 +255,7 @@ class _Single(Optimizer):
 
     def __init__(self, lr: float, param_shapes: Sequence, *, device=None, stream=None, **defaults):
         self._numel = [_numel_of(s) for s in param_shapes]
+        self._shapes = [_shape2d_of(s) for s in param_shapes]
         self._h = _Handle(device, stream)
         cfg = L.GroupConfig(kind=self._KIND, lr=float(lr), beta1=defaults.get("beta1", 0.0),
                             beta2=defaults.get("beta2", 0.0), eps=defaults.get("eps", 0.0),
@@ -302,7 +342,7 @@ class Sgd(_Single):
 
     # Sgd names its velocity v{i} (alg.rs:620-640); it lives in state slot 0 here
     def state_tensors(self):
-        return [(f"v{i}", self._h.state_export(i, 0, n)) for i, n in enumerate(self._numel)]
+        return [(f"v{i}", self._state(i, 0)) for i in range(len(self._numel))]
 
     def load_state_tensors(self, tensors):
         v = [None] * len(self._numel)
@@ -318,7 +358,9 @@ class Sgd(_Single):
         for i, t in enumerate(v):
             if t is None:
                 raise ValueError(f"missing v{i}")
-            self._h.state_import(i, 0, t.reshape(-1))
+        flat = [_flat_state(t, self._numel[i], f"v{i}") for i, t in enumerate(v)]
+        for i, t in enumerate(flat):
+            self._h.state_import(i, 0, t)
 
 
 def adamw_step(param: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.Tensor, lr: float, beta1: float,
@@ -452,6 +494,7 @@ class GroupOptimizer(Optimizer):
                  stream=None):
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
+        self._shapes = [_shape2d_of(s) for s in shapes]
         self._configs = kept
         self._gid_of = gid_of
         self._h = _Handle(device, stream)
@@ -494,12 +537,12 @@ class GroupOptimizer(Optimizer):
             idxs = [i for i, g in enumerate(self._gid_of) if g == gi]
             if cfg.kind == L.NBO_SGD:
                 for li, i in enumerate(idxs):
-                    out.append((f"g{gi}.v{li}", self._h.state_export(i, 0, self._numel[i])))
+                    out.append((f"g{gi}.v{li}", self._state(i, 0)))
             else:
                 for li, i in enumerate(idxs):
-                    out.append((f"g{gi}.m{li}", self._h.state_export(i, 0, self._numel[i])))
+                    out.append((f"g{gi}.m{li}", self._state(i, 0)))
                 for li, i in enumerate(idxs):
-                    out.append((f"g{gi}.v{li}", self._h.state_export(i, 1, self._numel[i])))
+                    out.append((f"g{gi}.v{li}", self._state(i, 1)))
         return out
 
 
@@ -636,6 +679,7 @@ class MixedAdamW:
         for the same bf16 params / fp32 master step."""
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
+        self._shapes = [_shape2d_of(s) for s in shapes]
         self._configs, self._gid_of = kept, gid_of
         self._grad_dtype = grad_dtype
         self._h = _Handle(device, stream)

@@ -15,7 +15,8 @@ from typing import Optional, Sequence, Tuple
 import torch
 
 from . import _lib as L
-from .optim import ParamGroupConfig, ParamSelector, StepOutcome, _Handle, _numel_of, assign_groups
+from .optim import (ParamGroupConfig, ParamSelector, StepOutcome, _flat_state, _Handle, _numel_of, _shape2d_of,
+                    assign_groups)
 
 
 def geometry(total: int, world: int) -> Tuple[int, int]:
@@ -68,6 +69,7 @@ class Zero1AdamW:
                  unique_id: Optional[bytes] = None, *, device=None, stream=None, timeout_s: Optional[float] = None):
         kept, gid_of = assign_groups(names, groups, default_group)
         self._numel = [_numel_of(s) for s in shapes]
+        self._shapes = [_shape2d_of(s) for s in shapes]
         self._configs, self._gid_of = kept, gid_of
         self.total = sum(self._numel)
         self.rank, self.world = rank, world
@@ -185,7 +187,8 @@ class Zero1AdamW:
     # ---- checkpoint: stitch the shards back into the reference's per-tensor state names ----------
     def state_tensors(self, group=None):
         """On rank 0: [(name, tensor)] with the names a GroupOptimizer uses (g{k}.m{i} / g{k}.v{i}) plus the
-        fp32 masters as g{k}.w{i}; None on the other ranks.  The shards travel through the host."""
+        fp32 masters as g{k}.w{i}, each with its parameter's (rows, cols); None on the other ranks.  The
+        shards travel through the host."""
         full = []
         for which in (0, 1, 2):
             shard = self.state_shard(which)
@@ -205,7 +208,7 @@ class Zero1AdamW:
             idx = [i for i, g in enumerate(self._gid_of) if g == gi]
             for which, p in ((0, "m"), (1, "v"), (2, "w")):
                 for li, i in enumerate(idx):
-                    out.append((f"g{gi}.{p}{li}", full[which][offs[i]:offs[i + 1]].clone()))
+                    out.append((f"g{gi}.{p}{li}", full[which][offs[i]:offs[i + 1]].clone().reshape(self._shapes[i])))
         return out
 
     def load_state_tensors(self, tensors) -> None:
@@ -213,7 +216,7 @@ class Zero1AdamW:
         offs = [0]
         for n in self._numel:
             offs.append(offs[-1] + n)
-        byname = {n: torch.as_tensor(t, dtype=torch.float32).reshape(-1) for n, t in tensors}
+        byname = {n: torch.as_tensor(t, dtype=torch.float32) for n, t in tensors}
         b = self.rank * self.shard
         for which, p in ((0, "m"), (1, "v"), (2, "w")):
             flat = torch.zeros(self.padded, dtype=torch.float32)
@@ -223,7 +226,7 @@ class Zero1AdamW:
                     key = f"g{gi}.{p}{li}"
                     if key not in byname:
                         raise ValueError(f"missing {p}{li}")
-                    flat[offs[i]:offs[i + 1]] = byname[key]
+                    flat[offs[i]:offs[i + 1]] = _flat_state(byname[key], self._numel[i], key)
             self.load_state_shard(which, flat[b:b + self.shard])
 
     def scaler_state(self) -> L.ScalerState:
