@@ -365,15 +365,26 @@ NBO_API int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat_bf16, void *g
                                int32_t average, int32_t use_scaler, double max_norm,
                                nbo_step_result *result);
 
-/* nbo_step_mixed_host for a ZeRO-1 handle of world size 1 (the single-GPU end
- * of the sharded configuration): device staging is the two flat buckets, the
- * host side is one pointer per tensor of the declared list (n = that list's
- * length).  With world > 1 it returns NBO_ERR_STATE: the reduce-scatter needs
- * every rank's whole bucket on the device before the first update. */
+/* nbo_step_mixed_host for a ZeRO-1 handle: the caller's gradients and parameters are host tensors (one
+ * pointer per tensor of the declared list, n = that list's length; alg.rs:109-150 reads `grads[i]` and
+ * writes `params[i]` in host memory on nabla's CPU backend) and the two flat buckets are device staging.
+ *   world == 1: exactly nbo_step_mixed_host on the flat buckets.
+ *   world  > 1: the buckets must be the ones given to nbo_zero1_attach_symmetric.  Every rank passes its own
+ *     gradients for the WHOLE list (data-parallel replicas) and receives the updated parameters of ITS
+ *     shard (the elements nbo_zero1_shard reports) in `params_host`; the other elements of `params_host`
+ *     are not written.  The shard is cut into slices of about `slice_elems` elements (0 = 32 Mi / world);
+ *     per slice every rank copies in its gradients for that slice of every rank's shard, a stream-ordered
+ *     barrier follows, the fused kernel reduces / updates / publishes the slice over NVLink, and the slice's
+ *     parameters are copied out - so PCIe (both directions) and NVLink work at the same time.  With
+ *     use_scaler or max_norm > 0 all gradients are copied in first and a skipped step copies nothing out.
+ *     Results are bit-identical to nbo_zero1_step_fused on the same gradients.  One bounded host wait per
+ *     step (nbo_zero1_set_timeout).
+ * `average` as in nbo_zero1_step (ignored when world == 1). */
 NBO_API int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, void *grads_flat_dev,
                                     uint64_t n, void *const *params_host,
                                     const void *const *grads_host, uint64_t slice_elems,
-                                    int32_t use_scaler, double max_norm, nbo_step_result *result);
+                                    int32_t average, int32_t use_scaler, double max_norm,
+                                    nbo_step_result *result);
 
 /* The same step with the two collectives fused into the kernels over NVLink /
  * NVSwitch peer memory instead of issued as separate NCCL passes.  Both flat
@@ -393,11 +404,23 @@ NBO_API int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local,
  * pass when loss scaling or clipping is on, per-rank scalars all-gathered and
  * combined in rank order] -> one kernel per group that reads the gradients of
  * this rank's shard from every rank, updates the fp32 state and writes the
- * bf16 params into every rank's bucket -> barrier.  The reduced gradients are
- * left in this rank's slice of its own gradient bucket, as nbo_zero1_step
- * leaves them.  Same result structure and skip semantics as nbo_zero1_step. */
+ * bf16 params into every rank's bucket -> barrier.  Everything is enqueued
+ * without waiting; the kernels that touch other ranks' memory verify on the
+ * device that the barrier before them completed (and do nothing otherwise), and
+ * the host waits once, at the end, with the nbo_zero1_set_timeout limit.  The
+ * reduced gradients are left in this rank's slice of its own gradient bucket,
+ * as nbo_zero1_step leaves them, unless nbo_zero1_keep_reduced_grads(h, 0).
+ * Same result structure and skip semantics as nbo_zero1_step. */
 NBO_API int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scaler,
                                      double max_norm, nbo_step_result *result);
+
+/* Whether the fused step also writes the reduced gradient into this rank's
+ * slice of its own gradient bucket (default 1, what an in-place reduce-scatter
+ * leaves behind; nabla-train/src/dist.rs:36-43 hands the mean back to the
+ * caller).  A caller that zeroes or overwrites the gradients after the step
+ * anyway can switch it off and save 2 bytes of HBM writes per element; a step
+ * with loss scaling or clipping always writes them (its two passes need them). */
+NBO_API int32_t nbo_zero1_keep_reduced_grads(nbo_optimizer *h, int32_t on);
 
 /* This rank's shard range in bucket elements and the number of table entries
  * (tensor pieces) it holds. */
@@ -425,6 +448,15 @@ NBO_API int32_t nbo_zero1_state_import(nbo_optimizer *h, int32_t which, const fl
  * (nabla-train/src/profiler.rs:177-197). */
 NBO_API int32_t nbo_profile(nbo_optimizer *h, int32_t on);
 NBO_API int32_t nbo_profile_last(nbo_optimizer *h, float *norm_ms, float *update_ms);
+
+/* Plain device-to-device copy of `bytes` bytes with 128-bit loads and stores
+ * issued by the SMs (persistent grid), asynchronous on `stream`; `src` or `dst`
+ * may be another GPU's memory mapped into this process.  It is the yardstick
+ * the NVLink share of the fused sharded step is measured against (same kind of
+ * access, nothing else to do); it has no counterpart in the reference.
+ * Pointers and size must be multiples of 16 bytes. */
+NBO_API int32_t nbo_copy_probe(int32_t device, void *stream, void *dst, const void *src,
+                               uint64_t bytes);
 
 /* Number of kernels the handle has launched since creation (all entry
  * points), and the number of chunks in its multi-tensor table. */

@@ -155,25 +155,113 @@ __device__ __forceinline__ void publish_elem(uint16_t *p_local, uint16_t v, cons
     for (int r = 0; r < pa.world; ++r) *(uint16_t *)((char *)p_local + pa.p_peer[r]) = v;
 }
 
+// The cross-rank barrier that precedes a peer-touching kernel is an NCCL all-reduce (max) of a sequence
+// number on the same stream.  If a rank has gone away the host's bounded wait aborts the communicator, the
+// collective ends without delivering the number, and the kernels queued behind it find a stale value here and
+// return without touching any other rank's memory.
+__device__ __forceinline__ bool barrier_passed(const PeerArgs &pa)
+{
+    return pa.barrier_seen == nullptr || *(const volatile int32_t *)pa.barrier_seen == pa.barrier_expect;
+}
+
+// 8-byte asynchronous copy global -> shared (LDGSTS; not the bulk / tensor-map engine).  Used to stage the
+// other ranks' gradients several chunks ahead without holding registers for them.
+__device__ __forceinline__ void cp_async_8(void *smem_dst, const void *gmem_src)
+{
+    uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+// Input transports of the fused update beyond enum Transport:
+//   kPeerRing  the other ranks' gradients of the next kRingStages-1 chunks are in flight to a shared-memory
+//              ring (cp.async, 8 bytes per thread and item; every thread reads back only what it copied
+//              itself, so no CTA barrier is needed).  Remote latency is then covered by up to
+//              2 CTAs x (kRingStages-1) x 8 KiB per remote rank in flight per SM, instead of by the
+//              loads of the chunk being worked on.  For world <= kRingMaxWorld.
+enum { kPeerRing = 3 };
+constexpr int kRingStages = 4;
+constexpr int kRingMaxWorld = 4;
+constexpr size_t ring_bytes(int world) { return (size_t)kRingStages * (size_t)(world - 1) * kChunkItems * sizeof(uint2); }
+
+struct ChunkLoc {
+    TensorDesc d;
+    ChunkView cv;
+};
+__device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
+                                                 uint32_t c)
+{
+    ChunkLoc l;
+    const Chunk ck = chunks[c];
+    l.d = descs[ck.tensor];
+    l.cv = chunk_view(l.d, ck);
+    return l;
+}
+
 // Fused reduce-scatter + Adam/AdamW + all-gather over this rank's shard.
-//   kIn  : where the gradient comes from - kLocal (already reduced into the
-//          local slice by an earlier pass), kPeer or kMcast (reduced here).
+//   kIn  : where the gradient comes from - kLocal (already reduced into the local slice by an earlier
+//          pass), kPeer (plain loads issued with the chunk, any world), kPeerRing (staged ahead through
+//          shared memory) or kMcast (multimem.ld_reduce, issued one chunk ahead into registers).
 //   kOut : how the bf16 params reach the other ranks - kPeer or kMcast.
+// All variants add the ranks' values in fp32 in rank order and round once, so kPeer and kPeerRing give
+// the same bits.
 template <int kIn, int kOut>
 __global__ void __launch_bounds__(kBlock)
 zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
                           uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl, PeerArgs pa)
 {
+    extern __shared__ __align__(16) unsigned char ring_raw[];
+    uint2 *ring = reinterpret_cast<uint2 *>(ring_raw);  // [stage][remote slot][kChunkItems]
+    if (!barrier_passed(pa))
+        return;
     float clip = 1.0f;
     if (ctrl != nullptr) {
         if (ctrl->skip)
             return;
         clip = ctrl->clip_scale;
     }
-    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const Chunk ck = chunks[c];
-        const TensorDesc d = descs[ck.tensor];
-        const ChunkView cv = chunk_view(d, ck);
+    const uint32_t mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int nremote = pa.world - 1;
+
+    // kPeerRing: start the copies of chunk number `it` of this CTA (an empty group when it does not exist)
+    auto stage_in = [&](uint32_t it) {
+        if (kIn == kPeerRing && it < mine) {
+            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
+            const char *g2 = (const char *)((const uint16_t *)l.d.g + l.cv.item0);
+            uint2 *dst = ring + (size_t)(it % kRingStages) * nremote * kChunkItems;
+            for (int q = 0; q < nremote; ++q) {
+                const char *src = g2 + pa.g_peer[q < pa.rank ? q : q + 1];
+#pragma unroll
+                for (int u = 0; u < kItemsPerThread; ++u) {
+                    uint32_t i = threadIdx.x + u * kBlock;
+                    if (i < l.cv.nitems) cp_async_8(dst + q * kChunkItems + i, src + (size_t)i * sizeof(uint2));
+                }
+            }
+        }
+        if (kIn == kPeerRing) cp_async_commit();
+    };
+    uint2 gq[kIn == kMcast ? kItemsPerThread : 1];  // kMcast: the reduced gradient of the next chunk
+    auto prefetch_mc = [&](uint32_t it) {
+        if (kIn == kMcast && it < mine) {
+            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
+            const uint2 *g2 = (const uint2 *)((const uint16_t *)l.d.g + l.cv.item0);
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < l.cv.nitems) gq[kIn == kMcast ? u : 0] = reduce_item<kMcast>(g2 + i, pa);
+            }
+        }
+    };
+    if (kIn == kPeerRing)
+        for (uint32_t it = 0; it + 1 < (uint32_t)kRingStages; ++it) stage_in(it);
+    prefetch_mc(0);
+
+    for (uint32_t it = 0; it < mine; ++it) {
+        const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
+        const TensorDesc &d = l.d;
+        const ChunkView &cv = l.cv;
         uint16_t *P = (uint16_t *)d.p;
         uint16_t *G = (uint16_t *)d.g;
         uint2 *p2 = (uint2 *)(P + cv.item0);
@@ -185,31 +273,50 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         uint2 g[kItemsPerThread];
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+        if (kIn == kMcast) {
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) g[u] = gq[kIn == kMcast ? u : 0];
+            prefetch_mc(it + 1);  // in flight while this chunk is updated and published
+        }
+        if (kIn == kPeerRing) stage_in(it + kRingStages - 1);
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn == kMcast) g[u] = reduce_item<kMcast>(g2 + i, pa);
-                if (kIn == kLocal) g[u] = ld_stream(g2 + i);
+                if (kIn == kLocal || kIn == kPeerRing) g[u] = ld_stream(g2 + i);  // ring: this rank's own term
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
                 v[u] = ld_stream(v4 + i);
             }
         }
+        if (kIn == kPeerRing) cp_async_wait<kRingStages - 1>();  // this chunk's group (and all older ones) has landed
+        const uint2 *slot = ring + (size_t)(it % kRingStages) * nremote * kChunkItems;
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn != kLocal) st_stream(g2 + i, g[u]);
+                if (kIn == kPeerRing) {
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                    for (int r = 0; r < pa.world; ++r) {  // rank order, as the plain peer path
+                        const uint2 x = r == pa.rank ? g[u] : slot[(r < pa.rank ? r : r - 1) * kChunkItems + i];
+                        a0 = __fadd_rn(a0, bf16_to_f32(x.x & 0xffffu));
+                        a1 = __fadd_rn(a1, bf16_to_f32(x.x >> 16));
+                        a2 = __fadd_rn(a2, bf16_to_f32(x.y & 0xffffu));
+                        a3 = __fadd_rn(a3, bf16_to_f32(x.y >> 16));
+                    }
+                    g[u].x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
+                    g[u].y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
+                }
+                if (kIn != kLocal && pa.keep_reduced) st_stream(g2 + i, g[u]);
                 mixed_elem<true>(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
                 uint2 o;
-                o.x = f32_to_bf16(w[u].x) | (f32_to_bf16(w[u].y) << 16);
-                o.y = f32_to_bf16(w[u].z) | (f32_to_bf16(w[u].w) << 16);
+                o.x = pack_bf16x2(w[u].x, w[u].y);
+                o.y = pack_bf16x2(w[u].z, w[u].w);
                 st_stream(w4 + i, w[u]);
                 st_stream(m4 + i, m[u]);
                 st_stream(v4 + i, v[u]);
@@ -220,12 +327,13 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
             for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
                 uint16_t gi = kIn == kLocal ? G[i] : reduce_elem(G + i, pa);
-                if (kIn != kLocal) G[i] = gi;
+                if (kIn != kLocal && pa.keep_reduced) G[i] = gi;
                 mixed_elem<true>(bf16_to_f32(gi), d.s2[i], d.s0[i], d.s1[i], hp, clip);
                 publish_elem(P + i, (uint16_t)f32_to_bf16(d.s2[i]), pa);
             }
         }
     }
+    if (kIn == kPeerRing) cp_async_wait<0>();
 }
 
 // Reduce-scatter fused with the norm / non-finite pass: the reduced gradient of
@@ -240,7 +348,8 @@ zero1_reduce_norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__re
 {
     double acc = 0.0;
     int bad = 0;
-    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const bool go = barrier_passed(pa);  // a failed barrier leaves every rank's memory alone; the partials still add up
+    for (uint32_t c = blockIdx.x; go && c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];
         const TensorDesc d = descs[ck.tensor];
         const ChunkView cv = chunk_view(d, ck);

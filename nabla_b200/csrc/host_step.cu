@@ -28,13 +28,6 @@
 
 namespace nbo {
 
-struct HostPipe {
-    cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t start = nullptr;
-    std::vector<cudaEvent_t> copied;   // gradients of slice s are on the device
-    std::vector<cudaEvent_t> updated;  // slice s has been updated
-};
-
 void host_pipe_destroy(nbo_optimizer *h)
 {
     HostPipe *p = h->host_pipe;
@@ -48,7 +41,7 @@ void host_pipe_destroy(nbo_optimizer *h)
     h->host_pipe = nullptr;
 }
 
-static int32_t ensure_pipe(nbo_optimizer *h, size_t nslices)
+int32_t host_pipe_ensure(nbo_optimizer *h, size_t nslices)
 {
     if (!h->host_pipe) {
         h->host_pipe = new (std::nothrow) HostPipe();
@@ -73,7 +66,7 @@ static int32_t ensure_pipe(nbo_optimizer *h, size_t nslices)
 
 // Drains the three streams after a failed enqueue so that no copy is still reading or
 // writing caller memory when the error is returned.
-static void drain(nbo_optimizer *h)
+void host_pipe_drain(nbo_optimizer *h)
 {
     HostPipe *p = h->host_pipe;
     if (p && p->in) cudaStreamSynchronize(p->in);
@@ -180,7 +173,7 @@ int32_t host_streamed_step(nbo_optimizer *h, void *const *host_p, const void *co
         if (sl.chunk_begin < h->groups[sl.group].chunk_begin || sl.chunk_end > h->groups[sl.group].chunk_end)
             return fail(h, NBO_ERR_STATE, "nabla-optim-b200: slice plan does not match the chunk list");
 
-    int32_t rc = ensure_pipe(h, plan.slices.size());
+    int32_t rc = host_pipe_ensure(h, plan.slices.size());
     if (rc != NBO_OK) return rc;
 
     const bool checked = use_scaler || max_norm > 0.0;
@@ -190,7 +183,7 @@ int32_t host_streamed_step(nbo_optimizer *h, void *const *host_p, const void *co
 
     rc = enqueue(h, plan, host_p, host_g, checked, inv_scale, max_norm);
     if (rc != NBO_OK) {
-        drain(h);
+        host_pipe_drain(h);
         return rc;
     }
     NBO_CUDA(h, cudaStreamSynchronize(h->stream));

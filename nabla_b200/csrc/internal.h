@@ -31,7 +31,14 @@ struct Piece {
 };
 
 struct Zero1;     // defined in zero1.cu
-struct HostPipe;  // defined in host_step.cu
+
+// Copy streams and events of the host-streamed steps (host_step.cu, zero1.cu), made on first use.
+struct HostPipe {
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr;
+    std::vector<cudaEvent_t> copied;   // gradients of slice s are on the device
+    std::vector<cudaEvent_t> updated;  // slice s has been updated
+};
 
 }  // namespace nbo
 
@@ -164,6 +171,12 @@ int32_t prof_mark(nbo_optimizer *h, int i);
 
 void zero1_destroy(nbo_optimizer *h);
 void host_pipe_destroy(nbo_optimizer *h);
+int32_t host_pipe_ensure(nbo_optimizer *h, size_t nslices);
+// Waits for the three streams after a failed enqueue, so that no copy still touches caller memory.
+void host_pipe_drain(nbo_optimizer *h);
+
+// One int written on the stream (the input of the cross-rank barrier).
+int32_t launch_store_int(nbo_optimizer *h, int32_t *dst, int32_t value);
 
 // Host-streamed mixed-precision step over the table as currently bound (host_step.cu).  `host_p` /
 // `host_g` hold one host pointer per caller tensor.

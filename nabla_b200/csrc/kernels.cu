@@ -1,6 +1,8 @@
 // The one translation unit that holds the device code, plus the launchers the
 // host code calls.  Grids are persistent: SM count x resident CTAs per SM
 // (from the occupancy calculator), capped by the number of chunks.
+#include <math.h>
+
 #include <map>
 #include <mutex>
 
@@ -86,19 +88,58 @@ int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const Adam
                 : launch_adam_mixed_one<false, false>(h, cb, nc, hp, nullptr, nullptr);
 }
 
+#ifndef NBO_NORM_CTAS_PER_SM
+#define NBO_NORM_CTAS_PER_SM 4
+#endif
+
+// Every norm launch of a handle uses the same grid whichever kernel variant runs (generic, per-element flag,
+// power-of-two scale): the per-thread accumulation order and the order of the per-CTA partials depend on the
+// grid alone, so the synchronous and the asynchronous step, and a step before and after the loss scale leaves
+// the power-of-two fast path, produce the same f64 sum for the same gradients.
+static int norm_grid(const nbo_optimizer *h)
+{
+    uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;  // one loop iteration takes kNormBatch chunks
+    long long g = (long long)h->sm_count * NBO_NORM_CTAS_PER_SM;
+    if (g > h->max_grid) g = h->max_grid;
+    if (g > (long long)units) g = units;
+    return (int)(g < 1 ? 1 : g);
+}
+
 template <bool kBf16, bool kCheckEach>
 static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, int finalize, const NormOut &out,
                             const float *inv_scale_dev = nullptr)
 {
-    uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;  // one loop iteration takes kNormBatch chunks
-    int grid = grid_for(h, units, (const void *)norm_kernel<kBf16, kCheckEach>);
+    int grid = norm_grid(h);
     norm_kernel<kBf16, kCheckEach><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
                                                                   inv_scale, max_norm, finalize, out, inv_scale_dev);
+}
+
+#ifndef NBO_NORM_VARIANT
+#define NBO_NORM_VARIANT 2  // 0 = always the generic kernel; 1..3 = norm_pow2_bf16_kernel<kVar> where it applies
+#endif
+
+// k with inv_scale == 2^-k exactly and 0 <= k <= 16 (the range in which the f32 product g * 2^-k is exact for
+// every finite bf16 g, so that the scale may be applied to the sum instead of to each element); -1 otherwise.
+static int pow2_unscale_exponent(float inv_scale)
+{
+    int e = 0;
+    if (!(inv_scale > 0.0f) || frexpf(inv_scale, &e) != 0.5f) return -1;
+    int k = 1 - e;  // inv_scale = 0.5 * 2^e = 2^(e-1)
+    return (k >= 0 && k <= 16) ? k : -1;
 }
 
 int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize)
 {
     NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
+    const int k = (bf16 && NBO_NORM_VARIANT != 0) ? pow2_unscale_exponent(inv_scale) : -1;
+    if (k >= 0) {
+        constexpr int kVar = NBO_NORM_VARIANT == 0 ? 2 : NBO_NORM_VARIANT;
+        Pow2Scale sc{ldexp(1.0, -2 * k), ldexp(1.0, -2 * k - 208)};
+        int grid = norm_grid(h);
+        norm_pow2_bf16_kernel<kVar><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, sc, max_norm,
+                                                                   finalize, out);
+        return launched(h);
+    }
     // the flag can be read off the sum only while the unscale factor cannot overflow a finite gradient
     bool each = !(inv_scale <= 1.0f);
     if (bf16) {
@@ -245,30 +286,60 @@ extern "C" int32_t nbo_adamw_step(int32_t device, void *stream, void *param, con
 
 // ---- ZeRO-1 fused with its collectives (fused_nvlink.cuh) ------------------------------------
 
+#ifndef NBO_PEER_RING
+#define NBO_PEER_RING 1  // 0 = the peer transport always issues its remote loads with the chunk (no staging ring)
+#endif
+
 namespace nbo {
 
 template <int kIn, int kOut>
 static int32_t launch_fused_one(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
                                 const PeerArgs &pa)
 {
-    int grid = grid_for(h, nc, (const void *)zero1_fused_update_kernel<kIn, kOut>);
-    zero1_fused_update_kernel<kIn, kOut><<<grid, kBlock, 0, h->stream>>>(
+    const void *k = (const void *)zero1_fused_update_kernel<kIn, kOut>;
+    size_t smem = kIn == kPeerRing ? ring_bytes(pa.world) : 0;
+    if (smem > 48 * 1024) {
+        static std::mutex once_lock;
+        static std::map<std::pair<const void *, int>, size_t> allowed;  // per kernel and device
+        std::lock_guard<std::mutex> guard(once_lock);
+        size_t &have = allowed[{k, h->device}];
+        if (have < smem) {
+            NBO_CUDA(h, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            have = smem;
+        }
+    }
+    // 2 resident CTAs per SM as for the local update kernel (register-limited; the ring fits twice as well)
+    int grid = grid_for(h, nc, k, 2);
+    zero1_fused_update_kernel<kIn, kOut><<<grid, kBlock, smem, h->stream>>>(
         h->d_descs, h->d_chunks + cb, nc, hp, with_ctrl ? h->d_ctrl : nullptr, pa);
     return launched(h);
 }
 
+// in_transport: 0 local, 1 peer (staged through the shared-memory ring when the world is small enough),
+// 2 multicast; out_transport: 1 peer stores, 2 multicast stores.
 int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
                                   const PeerArgs &pa, int in_transport, int out_transport)
 {
     if (nc == 0) return NBO_OK;
+    const bool ring = in_transport == kPeer && pa.world <= kRingMaxWorld && NBO_PEER_RING;
     if (out_transport == kMcast) {
         if (in_transport == kLocal) return launch_fused_one<kLocal, kMcast>(h, cb, nc, hp, with_ctrl, pa);
         if (in_transport == kMcast) return launch_fused_one<kMcast, kMcast>(h, cb, nc, hp, with_ctrl, pa);
+        if (ring) return launch_fused_one<kPeerRing, kMcast>(h, cb, nc, hp, with_ctrl, pa);
         return launch_fused_one<kPeer, kMcast>(h, cb, nc, hp, with_ctrl, pa);
     }
     if (in_transport == kLocal) return launch_fused_one<kLocal, kPeer>(h, cb, nc, hp, with_ctrl, pa);
     if (in_transport == kMcast) return launch_fused_one<kMcast, kPeer>(h, cb, nc, hp, with_ctrl, pa);
+    if (ring) return launch_fused_one<kPeerRing, kPeer>(h, cb, nc, hp, with_ctrl, pa);
     return launch_fused_one<kPeer, kPeer>(h, cb, nc, hp, with_ctrl, pa);
+}
+
+__global__ void store_int_kernel(int32_t *dst, int32_t value) { *dst = value; }
+
+int32_t launch_store_int(nbo_optimizer *h, int32_t *dst, int32_t value)
+{
+    store_int_kernel<<<1, 1, 0, h->stream>>>(dst, value);
+    return launched(h);
 }
 
 int32_t launch_zero1_reduce_norm(nbo_optimizer *h, float inv_scale, const PeerArgs &pa, int in_transport)
@@ -423,4 +494,45 @@ extern "C" int32_t nbo_grad_norm_noalloc(int32_t device, void *stream, const voi
     }();
     if (prev >= 0 && prev != device) cudaSetDevice(prev);
     return rc;
+}
+
+// ---- plain copy with SM loads and stores ------------------------------------------------------
+// The yardstick the NVLink fraction of the fused sharded step is quoted against: the same kind of access
+// the fused kernels make (128-bit loads and stores issued by SMs, persistent grid), with nothing else to do.
+// Either pointer may be another GPU's memory mapped into this process.
+
+namespace nbo {
+__global__ void __launch_bounds__(256) copy_probe_kernel(uint4 *__restrict__ dst, const uint4 *__restrict__ src, uint64_t n16)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * 256 * 4;
+    for (uint64_t i0 = (uint64_t)blockIdx.x * 1024 + threadIdx.x; i0 < n16; i0 += stride) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * 256 < n16) r[u] = src[i0 + u * 256];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * 256 < n16) dst[i0 + u * 256] = r[u];
+    }
+}
+}  // namespace nbo
+
+extern "C" int32_t nbo_copy_probe(int32_t device, void *stream, void *dst, const void *src, uint64_t bytes)
+{
+    using namespace nbo;
+    if (!dst || !src) return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_copy_probe: null pointer");
+    if ((((uintptr_t)dst | (uintptr_t)src) & 15u) || (bytes & 15u))
+        return fail(nullptr, NBO_ERR_INVALID, "nabla-optim-b200: nbo_copy_probe: pointers and size must be multiples of 16 bytes");
+    if (bytes == 0) return NBO_OK;
+    DeviceGuard guard(device);
+    int sms = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return fail_cuda(nullptr, e, "cudaDeviceGetAttribute");
+    uint64_t n16 = bytes / 16;
+    uint64_t want = (n16 + 1023) / 1024;
+    int grid = (int)(want < (uint64_t)sms * 8 ? want : (uint64_t)sms * 8);
+    copy_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((uint4 *)dst, (const uint4 *)src, n16);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(nullptr, e, "copy_probe_kernel");
+    return NBO_OK;
 }

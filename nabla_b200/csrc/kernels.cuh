@@ -466,6 +466,38 @@ __device__ __forceinline__ void write_ctrl(StepCtrl *ctrl, double sum, int bad, 
     *ctrl = c;
 }
 
+// Second half of the norm pass: one partial per CTA, then the last CTA to arrive (self-resetting ticket) adds
+// the partials in index order and writes the outputs.
+__device__ __forceinline__ void norm_finish(double acc, int bad, const NormOut &out, double max_norm, int finalize)
+{
+    double bsum = block_sum_f64(acc, bad);
+    __shared__ bool s_last;
+    if (threadIdx.x == 0) {
+        out.partial_sum[blockIdx.x] = bsum;
+        out.partial_bad[blockIdx.x] = bad;
+        __threadfence();
+        uint32_t t = atomicInc(out.ticket, gridDim.x - 1);  // wraps to 0 after the last CTA
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    double tot = 0.0;
+    int anybad = 0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kBlock) {
+        tot += __ldcg(out.partial_sum + i);
+        anybad |= __ldcg(out.partial_bad + i);
+    }
+    tot = block_sum_f64(tot, anybad);
+    if (threadIdx.x == 0) {
+        out.local[0] = tot;
+        out.local[1] = anybad ? 1.0 : 0.0;
+        if (finalize)
+            write_ctrl(out.ctrl, tot, anybad, max_norm);
+    }
+}
+
 // Sum-of-squares accumulation without a per-element flag: any inf/NaN among the
 // inputs makes the f64 sum itself non-finite (squares cannot cancel, and finite
 // f32 squares cannot overflow f64), so the flag is read off the total.  That
@@ -574,32 +606,145 @@ norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chun
     }
     acc += acc2;
     if (!kCheckEach) bad = (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN
-    double bsum = block_sum_f64(acc, bad);
-    __shared__ bool s_last;
-    if (threadIdx.x == 0) {
-        out.partial_sum[blockIdx.x] = bsum;
-        out.partial_bad[blockIdx.x] = bad;
-        __threadfence();
-        uint32_t t = atomicInc(out.ticket, gridDim.x - 1);  // wraps to 0 after the last CTA
-        s_last = (t == gridDim.x - 1);
+    norm_finish(acc, bad, out, max_norm, finalize);
+}
+
+// ---- bf16 norm pass for power-of-two unscale factors ------------------------------------------------
+// The generic kernel above spends one f32 multiply and one f32 -> f64 convert per element; the convert
+// runs on the quarter-rate conversion pipe and is what holds that kernel below the HBM roofline on bf16
+// input (2 bytes per element).  A loss scale is a power of two in practice (it starts at 2^16 and only
+// ever doubles or halves), and without a scaler the factor is 1, so here the factor 2^-k never touches an
+// element: squares of the raw values are accumulated and the exact power 2^-2k is applied once per
+// thread at the end.  For k <= 16 the reference's f32 product g * 2^-k is exact for every finite bf16 g
+// (the smallest bf16 subnormal, 2^-133, times 2^-16 is the smallest f32 subnormal), and scaling by a power
+// of two commutes with every rounding of the f64 accumulation (nothing under- or overflows: partial
+// sums stay within 2^-300 .. 2^500), so the sum has the same bits as the generic kernel's.
+//
+// The low half of each 32-bit word still goes through the convert; the high half is turned into an f64
+// with integer and FP64-pipe instructions only, which halves the load on the conversion pipe:
+//   bits = (w & 0x7fff0000) >> 3   placed in the high word of an f64 (low word zero) is |g| * 2^-896
+//          exactly, for normal, subnormal and zero g alike - bf16 and f64 share sign/exponent/mantissa
+//          order and the 3-bit shift moves the 8-bit exponent into the 11-bit field;
+//   y    = that * 2^1000           one exact FP64 multiply brings it back into the normal range
+//   acc2 = fma(y, y, acc2)         accumulates g^2 * 2^208, undone by the final scaling.
+// An inf/NaN in a high half is an ordinary finite number after this construction, so those are caught by
+// a running integer maximum of the masked words (one 3-input max per two words); low halves show in the
+// sum as before.  Accumulation order (low halves into `acc`, high halves into `acc2`) is the generic
+// kernel's.  kVar selects how many halves use the integer construction: 1 = none (convert only, scale
+// folded), 2 = high halves, 3 = both.
+struct Pow2Scale {
+    double lo;  // 2^-2k          applied to the chain of converted elements
+    double hi;  // 2^(-2k - 208)  applied to the chain of integer-built elements
+};
+
+__device__ __forceinline__ double bf16_bits_to_scaled_f64(uint32_t hi_word)
+{
+    return __hiloint2double((int)hi_word, 0) * 0x1p1000;
+}
+
+template <int kVar, bool kFull>
+__device__ __forceinline__ void norm_pow2_batch(const char *const (&base)[kNormBatch], const uint32_t (&nitems)[kNormBatch],
+                                                double &acc, double &acc2, uint32_t &mx)
+{
+    uint2 g[kNormBatch][kItemsPerThread];
+#pragma unroll
+    for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            uint32_t i = threadIdx.x + u * kBlock;
+            if (kFull || i < nitems[j]) g[j][u] = ld_stream((const uint2 *)base[j] + i);
+            else g[j][u] = make_uint2(0u, 0u);  // +0: adds nothing to either chain
+        }
+#pragma unroll
+    for (int j = 0; j < kNormBatch; ++j)
+#pragma unroll
+        for (int u = 0; u < kItemsPerThread; ++u) {
+            const uint32_t w0 = g[j][u].x, w1 = g[j][u].y;
+            if (kVar == 3) {
+                const uint32_t a0 = w0 & 0x7fff7fffu, a1 = w1 & 0x7fff7fffu;
+                mx = __vimax3_u16x2(mx, a0, a1);
+                double y;
+                y = bf16_bits_to_scaled_f64((a0 & 0xffffu) << 13); acc = fma(y, y, acc);
+                y = bf16_bits_to_scaled_f64(__umulhi(a0 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
+                y = bf16_bits_to_scaled_f64((a1 & 0xffffu) << 13); acc = fma(y, y, acc);
+                y = bf16_bits_to_scaled_f64(__umulhi(a1 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
+            } else {
+                double x, y;
+                x = (double)__uint_as_float(w0 << 16); acc = fma(x, x, acc);
+                if (kVar == 2) {
+                    const uint32_t t0 = w0 & 0x7fff0000u, t1 = w1 & 0x7fff0000u;
+                    mx = __vimax3_u32(mx, t0, t1);
+                    y = bf16_bits_to_scaled_f64(__umulhi(t0, 1u << 29)); acc2 = fma(y, y, acc2);
+                    x = (double)__uint_as_float(w1 << 16); acc = fma(x, x, acc);
+                    y = bf16_bits_to_scaled_f64(__umulhi(t1, 1u << 29)); acc2 = fma(y, y, acc2);
+                } else {
+                    x = (double)__uint_as_float(w0 & 0xffff0000u); acc2 = fma(x, x, acc2);
+                    x = (double)__uint_as_float(w1 << 16); acc = fma(x, x, acc);
+                    x = (double)__uint_as_float(w1 & 0xffff0000u); acc2 = fma(x, x, acc2);
+                }
+            }
+        }
+}
+
+template <int kVar>
+__global__ void __launch_bounds__(kBlock)
+norm_pow2_bf16_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks, uint32_t nchunks,
+                      Pow2Scale scale, double max_norm, int finalize, NormOut out)
+{
+    double acc = 0.0, acc2 = 0.0;
+    uint32_t mx = 0;
+    const uint32_t stride = gridDim.x * kNormBatch;
+    for (uint32_t c0 = blockIdx.x * kNormBatch; c0 < nchunks; c0 += stride) {
+        const char *base[kNormBatch];
+        uint32_t nitems[kNormBatch];
+        bool stray = false, full = true;
+#pragma unroll
+        for (int j = 0; j < kNormBatch; ++j) {
+            nitems[j] = 0;
+            base[j] = nullptr;
+            if (c0 + j < nchunks) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                base[j] = (const char *)d.g + cv.item0 * 2;
+                nitems[j] = cv.nitems;
+                stray |= (cv.s_lo1 > cv.s_lo0) | (cv.s_hi1 > cv.s_hi0);
+            }
+            full &= nitems[j] == kChunkItems;
+        }
+        if (full) norm_pow2_batch<kVar, true>(base, nitems, acc, acc2, mx);
+        else norm_pow2_batch<kVar, false>(base, nitems, acc, acc2, mx);
+        if (stray) {  // rare: head / tail elements one by one, through the convert, into the first chain
+            for (int j = 0; j < kNormBatch && c0 + j < nchunks; ++j) {
+                const Chunk ck = chunks[c0 + j];
+                const TensorDesc d = descs[ck.tensor];
+                const ChunkView cv = chunk_view(d, ck);
+                for (int r = 0; r < 2; ++r) {
+                    uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
+                    for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
+                        double x = (double)bf16_to_f32(((const uint16_t *)d.g)[i]);
+                        if (kVar == 3) {  // this variant's first chain carries the 2^208 factor
+                            x *= 0x1p104;
+                            if ((__double2hiint(x) & 0x7ff00000) == 0x7ff00000) mx = 0x7fff7fffu;
+                            else acc = fma(x, x, acc);
+                        } else {
+                            acc = fma(x, x, acc);
+                        }
+                    }
+                }
+            }
+        }
     }
-    __syncthreads();
-    if (!s_last)
-        return;
-    __threadfence();
-    double tot = 0.0;
-    int anybad = 0;
-    for (uint32_t i = threadIdx.x; i < gridDim.x; i += kBlock) {
-        tot += __ldcg(out.partial_sum + i);
-        anybad |= __ldcg(out.partial_bad + i);
+    int bad;
+    if (kVar == 3) {
+        bad = ((mx & 0xffffu) >= 0x7f80u || (mx >> 16) >= 0x7f80u) ? 1 : 0;
+        acc = acc * scale.hi + acc2 * scale.hi;
+    } else {
+        bad = (kVar == 2 && mx >= 0x7f800000u) ? 1 : 0;
+        acc = acc * scale.lo + acc2 * (kVar == 2 ? scale.hi : scale.lo);
     }
-    tot = block_sum_f64(tot, anybad);
-    if (threadIdx.x == 0) {
-        out.local[0] = tot;
-        out.local[1] = anybad ? 1.0 : 0.0;
-        if (finalize)
-            write_ctrl(out.ctrl, tot, anybad, max_norm);
-    }
+    bad |= (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN among the converted elements
+    norm_finish(acc, bad, out, max_norm, finalize);
 }
 
 // Non-finite test alone, for steps that use loss scaling but no clipping: no norm is needed then, only the

@@ -291,7 +291,7 @@ using namespace nbo;
 
 extern "C" {
 
-int32_t nbo_abi_version(void) { return 1; }
+int32_t nbo_abi_version(void) { return 2; }
 
 const char *nbo_last_error(const nbo_optimizer *h) { return h ? h->err.c_str() : g_err.c_str(); }
 

@@ -17,6 +17,7 @@
 #include <chrono>
 #include <thread>
 
+#include "host_plan.h"
 #include "internal.h"
 
 namespace nbo {
@@ -81,7 +82,9 @@ struct Zero1 {
     int transport = 0;             // 1 = plain peer loads/stores, 2 = NVSwitch multicast
     void *g_local = nullptr, *p_local = nullptr;
     PeerArgs pa{};
-    int32_t *d_barrier = nullptr;  // one int, all-reduced as a stream-ordered cross-rank barrier
+    int32_t *d_barrier = nullptr;  // [0] the sequence number this rank contributes, [1] the all-reduced (max) result
+    int32_t barrier_seq = 0;       // barriers enqueued so far; every rank enqueues the same ones in the same order
+    bool keep_reduced = true;      // the fused kernels also leave the reduced gradient in the local slice
 };
 
 static int32_t fail_nccl(nbo_optimizer *h, ncclResult_t r, const char *what)
@@ -153,6 +156,41 @@ static int32_t stream_wait(nbo_optimizer *h, Zero1 *z, const char *what)
         int32_t rc__ = nccl_wait((h), z, (call), #call);    \
         if (rc__ != NBO_OK) return rc__;                    \
     } while (0)
+
+// Stream-ordered cross-rank barrier: every rank writes the next sequence number and the ranks all-reduce it
+// (max).  *expect receives the number the result holds once the barrier has completed; kernels enqueued
+// behind it compare (barrier_passed in fused_nvlink.cuh) and leave peer memory alone when it has not.
+static int32_t enqueue_barrier(nbo_optimizer *h, Zero1 *z, int32_t *expect)
+{
+    NcclApi *a = nccl_api();
+    z->barrier_seq += 1;
+    int32_t rc = launch_store_int(h, z->d_barrier, z->barrier_seq);
+    if (rc != NBO_OK) return rc;
+    NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier + 1, 1, ncclInt32, ncclMax, z->comm, h->stream));
+    if (expect) *expect = z->barrier_seq;
+    return NBO_OK;
+}
+
+// The pieces (tensor intersections) of rank `rank`'s shard, in list order: the rows of that rank's table.
+static std::vector<Piece> shard_pieces(const std::vector<uint64_t> &numel, const std::vector<int32_t> &group_of,
+                                       int rank, uint64_t shard)
+{
+    std::vector<Piece> out;
+    const uint64_t begin = (uint64_t)rank * shard, end = begin + shard;
+    uint64_t off = 0;
+    for (size_t t = 0; t < numel.size(); ++t) {
+        uint64_t lo = off > begin ? off : begin;
+        uint64_t hi = off + numel[t] < end ? off + numel[t] : end;
+        if (hi > lo) {
+            Piece p;
+            p.tensor = t; p.offset = lo - off; p.n = hi - lo;
+            p.bucket_off = lo; p.state_off = lo - begin; p.group = group_of[t];
+            out.push_back(p);
+        }
+        off += numel[t];
+    }
+    return out;
+}
 
 void zero1_destroy(nbo_optimizer *h)
 {
@@ -245,21 +283,9 @@ int32_t nbo_zero1_init(nbo_optimizer *h, uint64_t n, const uint64_t *numel, cons
     h->numel.assign(numel, numel + n);
     h->group_of.resize(n);
     h->piece_of.assign(n, -1);
-    h->pieces.clear();
-    uint64_t off = 0;
-    for (uint64_t t = 0; t < n; ++t) {
-        h->group_of[t] = group_ids ? group_ids[t] : 0;
-        uint64_t lo = off > z->begin ? off : z->begin;
-        uint64_t hi = off + numel[t] < z->end ? off + numel[t] : z->end;
-        if (hi > lo) {
-            Piece p;
-            p.tensor = t; p.offset = lo - off; p.n = hi - lo;
-            p.bucket_off = lo; p.state_off = lo - z->begin; p.group = h->group_of[t];
-            h->piece_of[t] = (int64_t)h->pieces.size();
-            h->pieces.push_back(p);
-        }
-        off += numel[t];
-    }
+    for (uint64_t t = 0; t < n; ++t) h->group_of[t] = group_ids ? group_ids[t] : 0;
+    h->pieces = shard_pieces(h->numel, h->group_of, rank, z->shard);
+    for (size_t i = 0; i < h->pieces.size(); ++i) h->piece_of[h->pieces[i].tensor] = (int64_t)i;
     h->state_elems = z->shard;
     int32_t rc = build_table(h);
     if (rc != NBO_OK) { free_table(h); h->configured = false; zero1_destroy(h); return rc; }
@@ -361,20 +387,216 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
     return NBO_OK;
 }
 
+// Enqueues one fused sharded step on the attached buckets, up to and including the closing barrier and the
+// copy of the decision record; nothing here waits on the host.
+static int32_t enqueue_fused_step(nbo_optimizer *h, Zero1 *z, int32_t average, int32_t use_scaler, double max_norm)
+{
+    NcclApi *a = nccl_api();
+    PeerArgs pa = z->pa;
+    pa.average = average ? 1 : 0;
+    pa.keep_reduced = z->keep_reduced ? 1 : 0;
+    pa.barrier_seen = z->d_barrier + 1;
+
+    // every rank's gradients are final, and nobody still reads the old params, before any peer access
+    int32_t rc = enqueue_barrier(h, z, &pa.barrier_expect);
+    if (rc != NBO_OK) return rc;
+
+    bool checked = use_scaler || max_norm > 0.0;
+    float inv_scale = use_scaler ? (float)(1.0 / h->scaler.scale) : 1.0f;
+    h->prof_norm_valid = false;
+    int in_transport = z->transport;
+    if (checked) {
+        prof_mark(h, 0);
+        rc = launch_zero1_reduce_norm(h, inv_scale, pa, z->transport);
+        if (rc != NBO_OK) return rc;
+        prof_mark(h, 1);
+        NBO_NCCL(h, a->AllGather(h->d_local, z->d_gathered, 2, ncclDouble, z->comm, h->stream));
+        rc = launch_finalize_ranks(h, z->d_gathered, z->world, max_norm);
+        if (rc != NBO_OK) return rc;
+        in_transport = 0;  // the reduced gradient now sits in the local slice
+    }
+    prof_mark(h, 2);
+    for (Group &g : h->groups) {
+        uint32_t nc = g.chunk_end - g.chunk_begin;
+        if (nc == 0) continue;
+        AdamHP hp = adam_hparams(g.cfg, g.step_count + 1, inv_scale);
+        rc = launch_zero1_fused_update(h, g.chunk_begin, nc, hp, checked, pa, in_transport, z->transport);
+        if (rc != NBO_OK) return rc;
+    }
+    prof_mark(h, 3);
+    // every rank's parameter stores have landed everywhere before anyone uses the params
+    rc = enqueue_barrier(h, z, nullptr);
+    if (rc != NBO_OK) return rc;
+    if (checked)
+        NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
+                                    h->stream));
+    return NBO_OK;
+}
+
+// Host-streamed sharded step, world > 1, on the attached symmetric buckets.
+//
+// Every rank holds its own gradients for the WHOLE parameter list in host memory (data-parallel replicas)
+// and wants the updated parameters of its shard back in host memory.  Rank q's table is cut into slices of
+// about `slice_elems` elements; slice s of the step is "slice s of every rank's shard".  Per slice, on every rank:
+//   copy-in stream : this rank's host gradients for slice s of ALL ranks' shards -> its device bucket
+//   compute stream : barrier (all ranks have slice s on the device) -> fused kernel over this rank's
+//                    slice s (reads every rank's bucket, writes every rank's parameter bucket)
+//   copy-out stream: this rank's slice s of the parameters -> host
+// so the PCIe copies of slice s+1 run while slice s is reduced, updated and published over NVLink.  Every
+// rank derives every rank's slice boundaries from the declared sizes alone (same planner, same inputs), so
+// no geometry is exchanged.  With loss scaling or clipping the decision needs every gradient first: all
+// slices are copied in, the fused checked step runs, and the shard is copied out unless the step was skipped.
+static int32_t zero1_host_step_sharded(nbo_optimizer *h, Zero1 *z, void *const *host_p, const void *const *host_g,
+                                       uint64_t slice_elems, int32_t average, int32_t use_scaler, double max_norm,
+                                       nbo_step_result *result)
+{
+    for (uint64_t t = 0; t < h->ntensors; ++t)
+        if (h->numel[t] && (!host_p[t] || !host_g[t]))
+            return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null host pointer for tensor " + std::to_string(t));
+    if (slice_elems == 0) {  // 64 MiB of bf16 copied in per slice, but no slice shorter than 1 Mi elements
+        slice_elems = (32ull << 20) / (uint64_t)z->world;
+        if (slice_elems < (1ull << 20)) slice_elems = 1ull << 20;
+    }
+    const uint64_t slice_chunks = (slice_elems + kChunkElems - 1) / kChunkElems;
+
+    // every rank's rows and slice plan
+    std::vector<std::vector<Piece>> rows(z->world);
+    std::vector<HostPlan> plans(z->world);
+    size_t ns = 0;
+    for (int q = 0; q < z->world; ++q) {
+        rows[q] = q == z->rank ? h->pieces : shard_pieces(h->numel, h->group_of, q, z->shard);
+        const size_t np = rows[q].size();
+        std::vector<uint64_t> row_n(np);
+        std::vector<uint32_t> row_head(np);
+        std::vector<int32_t> row_group(np);
+        for (size_t i = 0; i < np; ++i) {
+            row_n[i] = rows[q][i].n;
+            row_head[i] = (uint32_t)((4 - (rows[q][i].bucket_off & 3)) & 3);  // as bind_flat sets it
+            row_group[i] = rows[q][i].group;
+        }
+        plans[q] = plan_host_slices(row_n, row_head, row_group, (int32_t)h->groups.size(), slice_chunks);
+        if (plans[q].slices.size() > ns) ns = plans[q].slices.size();
+    }
+    const HostPlan &mine = plans[z->rank];
+    for (const Slice &sl : mine.slices)
+        if (sl.chunk_begin < h->groups[sl.group].chunk_begin || sl.chunk_end > h->groups[sl.group].chunk_end)
+            return fail(h, NBO_ERR_STATE, "nabla-optim-b200: slice plan does not match the chunk list");
+
+    int32_t rc = host_pipe_ensure(h, ns ? ns : 1);
+    if (rc != NBO_OK) return rc;
+    HostPipe *pipe = h->host_pipe;
+    const bool checked = use_scaler || max_norm > 0.0;
+    uint16_t *gflat = (uint16_t *)z->g_local;
+    const uint16_t *pflat = (const uint16_t *)z->p_local;
+
+    auto copy_in = [&](size_t s) -> int32_t {
+        for (int q = 0; q < z->world; ++q) {
+            if (s >= plans[q].slices.size()) continue;
+            const Slice &sl = plans[q].slices[s];
+            for (uint32_t k = sl.copy_begin; k < sl.copy_end; ++k) {
+                const SliceCopy &c = plans[q].copies[k];
+                const Piece &pc = rows[q][c.row];
+                const char *src = (const char *)host_g[pc.tensor] + (pc.offset + c.lo) * 2;
+                NBO_CUDA(h, cudaMemcpyAsync(gflat + pc.bucket_off + c.lo, src, (c.hi - c.lo) * 2, cudaMemcpyHostToDevice,
+                                            pipe->in));
+            }
+        }
+        NBO_CUDA(h, cudaEventRecord(pipe->copied[s], pipe->in));
+        return NBO_OK;
+    };
+    auto copy_out = [&](size_t s) -> int32_t {
+        if (s >= mine.slices.size()) return NBO_OK;
+        const Slice &sl = mine.slices[s];
+        for (uint32_t k = sl.copy_begin; k < sl.copy_end; ++k) {
+            const SliceCopy &c = mine.copies[k];
+            const Piece &pc = h->pieces[c.row];
+            char *dst = (char *)host_p[pc.tensor] + (pc.offset + c.lo) * 2;
+            NBO_CUDA(h, cudaMemcpyAsync(dst, pflat + pc.bucket_off + c.lo, (c.hi - c.lo) * 2, cudaMemcpyDeviceToHost,
+                                        pipe->out));
+        }
+        return NBO_OK;
+    };
+
+    rc = [&]() -> int32_t {
+        // work already on the compute stream (the previous step's closing barrier above all) comes first
+        NBO_CUDA(h, cudaEventRecord(pipe->start, h->stream));
+        NBO_CUDA(h, cudaStreamWaitEvent(pipe->in, pipe->start, 0));
+        NBO_CUDA(h, cudaStreamWaitEvent(pipe->out, pipe->start, 0));
+        if (checked) {
+            for (size_t s = 0; s < ns; ++s) {
+                int32_t r = copy_in(s);
+                if (r != NBO_OK) return r;
+            }
+            if (ns) NBO_CUDA(h, cudaStreamWaitEvent(h->stream, pipe->copied[ns - 1], 0));
+            return enqueue_fused_step(h, z, average, use_scaler, max_norm);
+        }
+        PeerArgs pa = z->pa;
+        pa.average = average ? 1 : 0;
+        pa.keep_reduced = z->keep_reduced ? 1 : 0;
+        pa.barrier_seen = z->d_barrier + 1;
+        std::vector<AdamHP> hp(h->groups.size());
+        for (size_t g = 0; g < h->groups.size(); ++g) hp[g] = adam_hparams(h->groups[g].cfg, h->groups[g].step_count + 1, 1.0f);
+        h->prof_norm_valid = false;
+        for (size_t s = 0; s < ns; ++s) {
+            int32_t r = copy_in(s);
+            if (r != NBO_OK) return r;
+            NBO_CUDA(h, cudaStreamWaitEvent(h->stream, pipe->copied[s], 0));
+            r = enqueue_barrier(h, z, &pa.barrier_expect);
+            if (r != NBO_OK) return r;
+            if (s < mine.slices.size()) {
+                const Slice &sl = mine.slices[s];
+                r = launch_zero1_fused_update(h, sl.chunk_begin, sl.chunk_end - sl.chunk_begin, hp[sl.group], false, pa,
+                                              z->transport, z->transport);
+                if (r != NBO_OK) return r;
+            }
+            NBO_CUDA(h, cudaEventRecord(pipe->updated[s], h->stream));
+            NBO_CUDA(h, cudaStreamWaitEvent(pipe->out, pipe->updated[s], 0));
+            r = copy_out(s);
+            if (r != NBO_OK) return r;
+        }
+        return enqueue_barrier(h, z, nullptr);  // nobody overwrites gradients a peer may still be reading
+    }();
+    if (rc != NBO_OK) {
+        host_pipe_drain(h);  // an aborted communicator has already let its collectives return
+        return rc;
+    }
+    rc = stream_wait(h, z, "the host-streamed sharded step");  // the one bounded host wait of the step
+    if (rc != NBO_OK) return rc;
+    if (checked && !h->h_ctrl->nonfinite) {  // copy-out of the shard; a skipped step leaves the host parameters alone
+        for (size_t s = 0; s < mine.slices.size(); ++s) {
+            rc = copy_out(s);
+            if (rc != NBO_OK) { host_pipe_drain(h); return rc; }
+        }
+    }
+    NBO_CUDA(h, cudaStreamSynchronize(pipe->in));
+    NBO_CUDA(h, cudaStreamSynchronize(pipe->out));
+    commit_step(h, checked, use_scaler != 0, result);
+    return NBO_OK;
+}
+
 int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, void *grads_flat_dev, uint64_t n,
                             void *const *params_host, const void *const *grads_host, uint64_t slice_elems,
-                            int32_t use_scaler, double max_norm, nbo_step_result *result)
+                            int32_t average, int32_t use_scaler, double max_norm, nbo_step_result *result)
 {
     if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
     Zero1 *z = h->zero1;
-    if (z->world != 1)
-        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the host-streamed step is single-rank; with world > 1 "
-                                      "copy the gradient bucket in and call nbo_zero1_step");
     if (!params_flat_dev || !grads_flat_dev) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
     if (n != h->ntensors || (n && (!params_host || !grads_host)))
         return fail(h, NBO_ERR_INVALID, "nabla-train: params/grads length mismatch: " + std::to_string(n) +
                                             " host tensors for " + std::to_string(h->ntensors));
     DeviceGuard guard(h->device);
+    if (z->world > 1) {
+        if (!z->attached)
+            return fail(h, NBO_ERR_STATE, "nabla-optim-b200: with world > 1 the host-streamed step runs on the buckets "
+                                          "given to nbo_zero1_attach_symmetric");
+        if (params_flat_dev != z->p_local || grads_flat_dev != z->g_local)
+            return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: the device buckets must be the attached symmetric buckets");
+        if (z->broken)
+            return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
+        int32_t rc = bind_flat(h, z->p_local, z->g_local);
+        if (rc != NBO_OK) return rc;
+        return zero1_host_step_sharded(h, z, params_host, grads_host, slice_elems, average, use_scaler, max_norm, result);
+    }
     int32_t rc = bind_flat(h, params_flat_dev, grads_flat_dev);
     if (rc != NBO_OK) return rc;
     return host_streamed_step(h, params_host, grads_host, slice_elems, use_scaler, max_norm, result);
@@ -416,8 +638,8 @@ int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local, void *co
         pa.p_peer[r] = (int64_t)((intptr_t)params_peers[r] - (intptr_t)params_local);
     }
     if (!z->d_barrier) {
-        NBO_CUDA(h, cudaMalloc(&z->d_barrier, sizeof(int32_t)));
-        NBO_CUDA(h, cudaMemset(z->d_barrier, 0, sizeof(int32_t)));
+        NBO_CUDA(h, cudaMalloc(&z->d_barrier, 2 * sizeof(int32_t)));
+        NBO_CUDA(h, cudaMemset(z->d_barrier, 0, 2 * sizeof(int32_t)));
     }
     z->pa = pa; z->g_local = grads_local; z->p_local = params_local;
     z->transport = transport; z->attached = true;
@@ -434,51 +656,22 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
     if (z->broken) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
     cudaError_t ce = cudaSetDevice(h->device);
     if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
-    NcclApi *a = nccl_api();
     int32_t rc = bind_flat(h, z->p_local, z->g_local);
     if (rc != NBO_OK) return rc;
-    PeerArgs pa = z->pa;
-    pa.average = average ? 1 : 0;
-
-    // every rank's gradients are final, and nobody still reads the old params, before any peer access
-    NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, h->stream));
-    // The kernels below read and write the other ranks' memory.  They are enqueued only once the barrier is
-    // known to have completed, so a rank that has gone away ends this call with a timeout before anything
-    // touches its memory.
-    rc = stream_wait(h, z, "the barrier before the fused step");
+    // Everything is stream-ordered behind the opening barrier; the kernels that touch other ranks' memory
+    // check on the device that the barrier really completed, so the host waits once, at the end.
+    rc = enqueue_fused_step(h, z, average, use_scaler, max_norm);
     if (rc != NBO_OK) return rc;
-
-    bool checked = use_scaler || max_norm > 0.0;
-    float inv_scale = use_scaler ? (float)(1.0 / h->scaler.scale) : 1.0f;
-    h->prof_norm_valid = false;
-    int in_transport = z->transport;
-    if (checked) {
-        prof_mark(h, 0);
-        rc = launch_zero1_reduce_norm(h, inv_scale, pa, z->transport);
-        if (rc != NBO_OK) return rc;
-        prof_mark(h, 1);
-        NBO_NCCL(h, a->AllGather(h->d_local, z->d_gathered, 2, ncclDouble, z->comm, h->stream));
-        rc = launch_finalize_ranks(h, z->d_gathered, z->world, max_norm);
-        if (rc != NBO_OK) return rc;
-        in_transport = 0;  // the reduced gradient now sits in the local slice
-    }
-    prof_mark(h, 2);
-    for (Group &g : h->groups) {
-        uint32_t nc = g.chunk_end - g.chunk_begin;
-        if (nc == 0) continue;
-        AdamHP hp = adam_hparams(g.cfg, g.step_count + 1, inv_scale);
-        rc = launch_zero1_fused_update(h, g.chunk_begin, nc, hp, checked, pa, in_transport, z->transport);
-        if (rc != NBO_OK) return rc;
-    }
-    prof_mark(h, 3);
-    // every rank's parameter stores have landed everywhere before anyone uses the params
-    NBO_NCCL(h, a->AllReduce(z->d_barrier, z->d_barrier, 1, ncclInt32, ncclSum, z->comm, h->stream));
-    if (checked)
-        NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
-                                    h->stream));
     rc = stream_wait(h, z, "the fused sharded step");
     if (rc != NBO_OK) return rc;
-    commit_step(h, checked, use_scaler != 0, result);
+    commit_step(h, use_scaler || max_norm > 0.0, use_scaler != 0, result);
+    return NBO_OK;
+}
+
+int32_t nbo_zero1_keep_reduced_grads(nbo_optimizer *h, int32_t on)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    h->zero1->keep_reduced = on != 0;
     return NBO_OK;
 }
 

@@ -124,14 +124,21 @@ class Zero1AdamW:
         return StepOutcome.from_c(res)
 
     def step_host_ptrs(self, params_ptr: int, grads_ptr: int, params_host_arr, grads_host_arr, *,
-                       use_scaler=False, max_norm=0.0, slice_elems=0) -> StepOutcome:
-        """World size 1 only: gradients come from, and parameters return to, HOST tensors (one pointer per
-        declared tensor, `_lib.ptr_array`), pipelined slice by slice through the two flat device buckets."""
+                       average=False, use_scaler=False, max_norm=0.0, slice_elems=0) -> StepOutcome:
+        """Gradients come from, and parameters return to, HOST tensors (one pointer per declared tensor,
+        `_lib.ptr_array`), pipelined slice by slice through the two flat device buckets.  With world > 1 the
+        buckets are the attached symmetric ones, every rank passes its own gradients for the whole list and
+        gets the parameters of its own shard back."""
         res = L.StepResult()
         self._h.check(self._h.lib.nbo_zero1_step_host(
             self._h.h, C.c_void_p(params_ptr), C.c_void_p(grads_ptr), len(params_host_arr), params_host_arr,
-            grads_host_arr, int(slice_elems), 1 if use_scaler else 0, float(max_norm), C.byref(res)))
+            grads_host_arr, int(slice_elems), 1 if average else 0, 1 if use_scaler else 0, float(max_norm),
+            C.byref(res)))
         return StepOutcome.from_c(res)
+
+    def keep_reduced_grads(self, on: bool) -> None:
+        """Fused step: whether the reduced gradient is also written into this rank's slice of its bucket."""
+        self._h.check(self._h.lib.nbo_zero1_keep_reduced_grads(self._h.h, 1 if on else 0))
 
     # ---- fused path over NVLink / NVSwitch peer memory -------------------------------------------
     def attach_symmetric(self, group=None, transport: int = 0):

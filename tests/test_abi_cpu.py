@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol(nbo_lib):
     for s in syms:
         assert hasattr(nbo_lib, s), f"{s} declared in the header but not exported"
     assert sorted(_lib.SIGNATURES) == syms, "Python binding and header disagree"
-    assert nbo_lib.nbo_abi_version() == 1
+    assert nbo_lib.nbo_abi_version() == 2
 
 
 def test_library_has_no_link_dependency_on_nccl_or_oracle():

@@ -223,6 +223,66 @@ def test_large_norm_and_exact_flag(nb):
     assert norm(g)[1] is False
 
 
+@pytest.mark.parametrize("scale", [1.0, 2.0, 65536.0, 131072.0, 3.0])
+def test_power_of_two_norm_pass_has_the_generic_kernels_bits(nb, scale):
+    """With an unscale factor 2^-k, k <= 16, the synchronous step takes its norm from the kernel that builds
+    f64 values by bit placement and applies the scale to the sum; the asynchronous step (scale read from
+    device memory) always runs the generic kernel that multiplies and converts every element.  Same grid,
+    same accumulation order: the two norms must be the same f64, on data that holds zeros, bf16 and f32
+    subnormals, the largest finite value and ordinary gradients, over several tensors with ragged ends.
+    Scales 2^17 and 3 take the generic kernel on both sides."""
+    sizes = [(1 << 24) + 3, 4096, 5, (1 << 22) - 1, 12345]
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    gs = []
+    for n in sizes:
+        g = (torch.randn(n, device="cuda", generator=gen) * 1e-3 * scale).to(torch.bfloat16)
+        bits = g.view(torch.int16)
+        idx = torch.arange(n, device="cuda")
+        bits[idx % 7 == 0] = 0                                   # +0
+        bits[idx % 11 == 0] = -32768                             # -0
+        bits[idx % 13 == 0] = 0x0001                             # smallest bf16 subnormal
+        bits[idx % 17 == 0] = 0x007f                             # largest bf16 subnormal
+        bits[idx % 19 == 0] = 0x0080                             # smallest normal: times 2^-16 is an f32 subnormal
+        bits[idx % 23 == 0] = -32768 + 0x0b00                    # a tiny negative normal
+        gs.append(g)
+    gs[1].view(torch.int16)[17] = 0x7f7f                         # largest finite bf16 (its square overflows f32)
+    ps = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+
+    def fresh():
+        o = nb.MixedAdamW.adamw(0.0, 0.0, [(n,) for n in sizes])  # lr 0: only the norm matters here
+        st = o.scaler_state(); st.scale = scale; o.load_scaler_state(st)
+        return o
+    a, b = fresh(), fresh()
+    P = nb._lib.ptr_array
+    rb = b.step(ps, gs, use_scaler=True, max_norm=1.0)
+    a.step_async(P([t.data_ptr() for t in ps]), P([t.data_ptr() for t in gs]), use_scaler=True, max_norm=1.0)
+    ra = a.collect()[0]
+    assert rb.applied and ra.applied and rb.grad_norm > 0.0
+    assert ra.grad_norm == rb.grad_norm, (ra.grad_norm.hex(), rb.grad_norm.hex())
+    # against exact integer arithmetic: every square is a dyadic rational, summed without rounding
+    from fractions import Fraction
+    if scale in (1.0, 65536.0):
+        exact = Fraction(0)
+        pick = [1, 2, 4]                                         # the small tensors, exactly
+        for t in pick:
+            for v in gs[t].float().cpu().tolist():
+                exact += Fraction(v) * Fraction(v)
+        small = nb.MixedAdamW.adamw(0.0, 0.0, [(sizes[t],) for t in pick])
+        st = small.scaler_state(); st.scale = scale; small.load_scaler_state(st)
+        r = small.step([ps[t] for t in pick], [gs[t] for t in pick], use_scaler=True, max_norm=1.0)
+        want = float(exact) ** 0.5 / scale
+        assert abs(r.grad_norm - want) <= 1e-14 * want, (r.grad_norm, want)
+    # a non-finite value in a low half and in a high half of a word, in the bulk and in a ragged tail
+    for t, i in ((0, 1000), (0, 1001), (0, sizes[0] - 1), (3, sizes[3] - 2)):
+        keep = gs[t][i].clone()
+        for v in (float("inf"), float("nan")):
+            gs[t][i] = v
+            r = fresh().step(ps, gs, use_scaler=True, max_norm=1.0)
+            assert not r.applied and r.nonfinite, (t, i, v)
+        gs[t][i] = keep
+    assert fresh().step(ps, gs, use_scaler=True, max_norm=1.0).applied
+
+
 @pytest.mark.parametrize("offset", [0, 1])
 def test_fp32_gradient_variant_versus_oracle(nb, oracle, offset):
     """bf16 params + fp32 gradients (accumulated in fp32): GradScaler -> clip -> AdamW on the masters -> cast,

@@ -87,6 +87,24 @@ def test_multi_gpu_matches_single_gpu(world, mode):
     assert "ZERO1_WORKER_OK" in r.stdout
 
 
+@pytest.mark.parametrize("mode", ["peer", "mcast"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_host_streamed_sharded_step_equals_the_fused_step(world, mode):
+    """nbo_zero1_step_host at world > 1: sliced copy-in / barrier / fused kernel / copy-out pipeline, bit for bit
+    the result of nbo_zero1_step_fused (tests/zero1_host_worker.py)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    port = 29600 + world + (20 if mode == "mcast" else 0)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(ROOT, "tests", "zero1_host_worker.py"), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    if "ZERO1_HOST_SKIP" in r.stdout:
+        pytest.skip(r.stdout.strip().splitlines()[-1])
+    assert "ZERO1_HOST_OK" in r.stdout
+
+
 def test_rank_that_never_arrives_times_out(nb):
     """Communicator set-up with a peer that never calls in: NBO_ERR_TIMEOUT after the limit, context intact."""
     import ctypes as C

@@ -6,7 +6,14 @@ nccl  : reduce-scatter / all-gather issued as NCCL collectives around the local 
 peer  : collectives fused into the kernels with plain peer loads/stores (nbo_zero1_step_fused, transport 1)
 mcast : the same through NVSwitch multimem ld_reduce / st (transport 2)
 
-Every rank holds its own bf16 gradients.  After N sharded steps each rank checks that
+Every rank holds its own bf16 gradients.  Each sharded step is checked three ways:
+  (0) the cross-rank reduction against an independent reference: every rank's INPUT gradients are
+      all-gathered before the step, this rank's shard is summed in fp32 in rank order with torch on local
+      memory, multiplied by f32(1/world) when averaging (the mean of the replicas,
+      nabla-train/src/dist.rs:36-43) and rounded once to bf16.  The reduced gradients the step leaves in
+      place must equal that bit for bit on the `peer` transport (same order, one rounding) and stay within
+      the rounding bounds of the other summation orders for `mcast` (the switch rounds to bf16 once, the
+      averaging rounds again: 1 ulp) and `nccl` (bf16 roundings between the ring's hops);
   (1) the parameter bucket is identical on all ranks, and
   (2) a world = 1 optimizer on the same GPU, fed the reduced gradients the sharded step actually used
       (gathered from the in-place reduce-scatter output), produces bit-identical parameters - i.e.
@@ -21,6 +28,45 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 import nabla_b200 as nb  # noqa: E402
+
+
+def ordered(bits16: torch.Tensor) -> torch.Tensor:
+    """bf16 bit patterns as integers that increase with the value (one step = one ulp)."""
+    i = bits16.view(torch.int16).to(torch.int32) & 0xffff
+    return torch.where(i >= 0x8000, 0x8000 - i, i)
+
+
+def check_reduction(mode, world, rank, raw, reduced, b, e, average, total):
+    """`raw`: every rank's input bucket; `reduced`: this rank's slice after the step."""
+    hi = min(e, total)
+    if hi <= b:
+        return
+    acc = torch.zeros(hi - b, dtype=torch.float32, device="cuda")
+    mag = torch.zeros_like(acc)
+    for r in range(world):                                   # rank order, one fp32 rounding per addition
+        x = raw[r][b:hi].float()
+        acc += x
+        mag += x.abs()
+    if average:
+        acc *= torch.tensor(1.0, dtype=torch.float32, device="cuda") / torch.tensor(float(world), dtype=torch.float32,
+                                                                                     device="cuda")
+    want = acc.to(torch.bfloat16)
+    got = reduced[:hi - b]
+    if mode == "peer":
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), \
+            f"rank {rank}: peer reduction differs from the fp32 rank-order sum"
+        return
+    ulps = (ordered(got) - ordered(want)).abs()
+    err = (got.float() - want.float()).abs()
+    if mode == "mcast":
+        ok = (ulps <= 1) | (err <= mag * 2.0 ** -20)
+    else:                                                    # nccl: a bf16 rounding per hop, each on a partial sum <= mag
+        ok = err <= mag * (world * 2.0 ** -8) * (1.0 / world if average else 1.0) + 1e-30
+    assert bool(ok.all()), (f"rank {rank} {mode}: reduced gradient off: worst {int(ulps.max())} ulp, "
+                            f"{int((~ok).sum())} elements outside the bound")
+    if rank == 0:
+        print(f"ZERO1_REDUCTION {mode} world {world} average {average}: worst {int(ulps.max())} ulp, "
+              f"{float((ulps > 0).float().mean()):.4f} of elements differ", flush=True)
 
 
 def main():
@@ -68,10 +114,13 @@ def main():
         for use_scaler, max_norm in ((False, 0.0),):
             gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
             gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4).to(torch.bfloat16)
+            raw = [torch.empty_like(gflat) for _ in range(world)]
+            dist.all_gather(raw, gflat)                          # every rank's input, before anything is reduced
             res, gflat = do_step(gflat, average=(step != 1), use_scaler=use_scaler, max_norm=max_norm)
             assert res.applied
             # the reduced gradients each rank used sit in its slice of gflat
             b, e, _ = z.shard_range()
+            check_reduction(mode, world, rank, raw, gflat[b:e], b, e, step != 1, total)
             parts = [torch.empty(z.shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
             dist.all_gather(parts, gflat[b:e].contiguous())
             gfull = torch.cat(parts)[:ref.padded].contiguous()
@@ -90,8 +139,12 @@ def main():
     assert torch.equal(before.view(torch.int16), pflat.view(torch.int16))
     gflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
     gflat[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4 * 32768).to(torch.bfloat16)
+    raw = [torch.empty_like(gflat) for _ in range(world)]
+    dist.all_gather(raw, gflat)
     res, gflat = do_step(gflat, average=True, use_scaler=True, max_norm=1e-3)
     assert res.applied and res.grad_norm > 1e-3
+    b, e, _ = z.shard_range()
+    check_reduction(mode, world, rank, raw, gflat[b:e], b, e, True, total)   # the reduce + norm kernel's output
     # the clipped, unscaled step against the single-GPU twin fed the same reduced gradients
     b, e, _ = z.shard_range()
     parts = [torch.empty(z.shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
