@@ -364,9 +364,8 @@ def peer_copy_peak(nb, opt, rank, world, dev, nbytes=1 << 30, reps=5):
 
     import torch
     import torch.distributed as dist
-    gh = opt._symm[3]
     nbytes = min(nbytes, opt.padded * 2) // 16 * 16
-    src = gh.buffer_ptrs[(rank + 1) % world]
+    src = opt.peer_grad_ptrs[(rank + 1) % world]
     dst = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
     lib = nb._lib.load()
     stream = torch.cuda.current_stream().cuda_stream
@@ -715,13 +714,16 @@ def run_ours(args, wl_name, wl):
 
     # end to end with host buffers
     e2e_steps = max(1, min(args.steps, 10))
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    if args.no_e2e:                                               # kernel experiments only: the line then has no e2e number
+        e2e_steps, e2e_s = 0, float("inf")
+    else:
         e2e_step()
-    barrier()
-    e2e_s = max_over_ranks((time.perf_counter() - t0)) / e2e_steps
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = max_over_ranks((time.perf_counter() - t0)) / e2e_steps
 
     # the 8 G-parameter step with dynamic loss scaling and clipping on (norm / non-finite pass + scaled update)
     scaled = None
@@ -852,6 +854,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama8b_zero1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-copy-probe", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (kernel experiments)")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table of the default line")
     ap.add_argument("--zero1-path", choices=["auto", "peer", "mcast", "nccl"], default="auto",
                     help="N > 1: collectives fused into the kernels (auto/peer/mcast) or issued through NCCL")

@@ -400,6 +400,32 @@ NBO_API int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local,
                                            void *params_local, void *const *params_peers,
                                            void *params_mc, int32_t transport);
 
+/* Symmetric buckets without any framework.  nbo_zero1_attach_symmetric needs every rank's bucket mapped
+ * into every process; these calls make such buckets with the CUDA virtual-memory API: one allocation per
+ * rank, mapped over NVLink into all ranks of the node and, where the fabric supports it (and
+ * want_multicast != 0), bound to one NVSwitch multicast object.  The ranks are processes of one node.
+ *   nbo_symm_token  rank 0 makes a 16-byte token and ships it to the other ranks by any host channel
+ *                   (as with the NCCL unique id); one token serves any number of allocations.
+ *   nbo_symm_alloc  collective: every rank calls it with the same token, tag, world and size.  The
+ *                   allocations' shareable handles are file descriptors, which a byte channel cannot
+ *                   carry, so the library passes them itself over abstract unix sockets named after
+ *                   token and tag (two allocations alive at once need different tags).  Every wait is
+ *                   bounded by timeout_s (<= 0: 60 s); on expiry NBO_ERR_TIMEOUT and nothing is kept.
+ *   nbo_symm_pointers  this process's mappings: *local (== peers[rank]), peers[0..world), and *multicast
+ *                   (NULL when the fabric has none) - the arguments of nbo_zero1_attach_symmetric.
+ *   nbo_symm_free   unbinds from the multicast object, unmaps and releases.  Every rank must call it
+ *                   (after its last use, e.g. after a barrier) before it exits: a process must not end
+ *                   while its memory is bound to a multicast object.
+ * The memory is zero-initialised device memory like any other; world <= 16.  Replaces the in-process
+ * channel pair of nabla-train/src/dist.rs:7-34 as the way replicas reach each other's buffers. */
+typedef struct nbo_symm nbo_symm;
+NBO_API int32_t nbo_symm_token(uint8_t token_out[16]);
+NBO_API int32_t nbo_symm_alloc(int32_t device, int32_t rank, int32_t world, uint64_t bytes,
+                               const uint8_t token[16], int32_t tag, int32_t want_multicast,
+                               double timeout_s, nbo_symm **out);
+NBO_API int32_t nbo_symm_pointers(const nbo_symm *s, void **local, void **peers, void **multicast);
+NBO_API int32_t nbo_symm_free(nbo_symm *s);
+
 /* One step on the attached buckets: stream-ordered barrier -> [reduce + norm
  * pass when loss scaling or clipping is on, per-rank scalars all-gathered and
  * combined in rank order] -> one kernel per group that reads the gradients of

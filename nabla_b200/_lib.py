@@ -100,6 +100,11 @@ SIGNATURES = {
     "nbo_zero1_step_host": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_uint64, _PP, _PP, C.c_uint64, C.c_int32,
                                         C.c_int32, C.c_double, C.POINTER(StepResult)]),
     "nbo_zero1_keep_reduced_grads": (C.c_int32, [_H, C.c_int32]),
+    "nbo_symm_token": (C.c_int32, [C.c_void_p]),
+    "nbo_symm_alloc": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_uint64, C.c_void_p, C.c_int32, C.c_int32,
+                                   C.c_double, C.POINTER(C.c_void_p)]),
+    "nbo_symm_pointers": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), _PP, C.POINTER(C.c_void_p)]),
+    "nbo_symm_free": (C.c_int32, [C.c_void_p]),
     "nbo_copy_probe": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
     "nbo_zero1_attach_symmetric": (C.c_int32, [_H, C.c_void_p, _PP, C.c_void_p, C.c_void_p, _PP, C.c_void_p,
                                                C.c_int32]),

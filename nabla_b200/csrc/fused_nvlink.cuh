@@ -182,7 +182,10 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 //              2 CTAs x (kRingStages-1) x 8 KiB per remote rank in flight per SM, instead of by the
 //              loads of the chunk being worked on.  For world <= kRingMaxWorld.
 enum { kPeerRing = 3 };
-constexpr int kRingStages = 4;
+#ifndef NBO_RING_STAGES
+#define NBO_RING_STAGES 4
+#endif
+constexpr int kRingStages = NBO_RING_STAGES;
 constexpr int kRingMaxWorld = 4;
 constexpr size_t ring_bytes(int world) { return (size_t)kRingStages * (size_t)(world - 1) * kChunkItems * sizeof(uint2); }
 

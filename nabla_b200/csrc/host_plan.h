@@ -65,6 +65,36 @@ struct HostPlan {
     std::vector<SliceCopy> copies;
 };
 
+// One table row of a ZeRO-1 rank: the part of tensor `tensor` that falls into the rank's shard.
+struct ShardRow {
+    uint64_t tensor;      // index in the declared list
+    uint64_t offset;      // first element of the piece inside its tensor
+    uint64_t n;           // elements
+    uint64_t bucket_off;  // element offset in the flat bucket
+    int32_t group;
+};
+
+// The rows of rank `rank` for a flat bucket holding the tensors in list order, every rank owning `shard`
+// consecutive elements.  Every rank can derive every other rank's rows (and from them its slice plan):
+// the result depends on the declared sizes alone.
+inline std::vector<ShardRow> shard_rows(const std::vector<uint64_t> &numel, const std::vector<int32_t> &group_of,
+                                        int rank, uint64_t shard)
+{
+    std::vector<ShardRow> out;
+    const uint64_t begin = (uint64_t)rank * shard, end = begin + shard;
+    uint64_t off = 0;
+    for (size_t t = 0; t < numel.size(); ++t) {
+        uint64_t lo = off > begin ? off : begin;
+        uint64_t hi = off + numel[t] < end ? off + numel[t] : end;
+        if (hi > lo) out.push_back(ShardRow{(uint64_t)t, lo - off, hi - lo, lo, group_of[t]});
+        off += numel[t];
+    }
+    return out;
+}
+
+// Leading elements of a bucket row that precede the next 4-element boundary of the bucket.
+inline uint32_t bucket_row_head(uint64_t bucket_off) { return (uint32_t)((4 - (bucket_off & 3)) & 3); }
+
 // Rows are given in chunk-list order: the list holds group 0's rows first (each row's chunks
 // consecutive, rows in table order), then group 1's, and so on.  `row_n`, `row_head`,
 // `row_group` are indexed by table row; `slice_chunks` >= 1 is the slice length in chunks.

@@ -642,6 +642,14 @@ __device__ __forceinline__ double bf16_bits_to_scaled_f64(uint32_t hi_word)
     return __hiloint2double((int)hi_word, 0) * 0x1p1000;
 }
 
+// bf16 -> f64 in one conversion instruction (exact for every input, inf / NaN included).
+__device__ __forceinline__ double bf16_half_to_f64(uint16_t h)
+{
+    double x;
+    asm("cvt.f64.bf16 %0, %1;" : "=d"(x) : "h"(h));
+    return x;
+}
+
 template <int kVar, bool kFull>
 __device__ __forceinline__ void norm_pow2_batch(const char *const (&base)[kNormBatch], const uint32_t (&nitems)[kNormBatch],
                                                 double &acc, double &acc2, uint32_t &mx)
@@ -668,6 +676,20 @@ __device__ __forceinline__ void norm_pow2_batch(const char *const (&base)[kNormB
                 y = bf16_bits_to_scaled_f64(__umulhi(a0 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
                 y = bf16_bits_to_scaled_f64((a1 & 0xffffu) << 13); acc = fma(y, y, acc);
                 y = bf16_bits_to_scaled_f64(__umulhi(a1 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
+            } else if (kVar == 4) {
+                double x;
+                x = bf16_half_to_f64((uint16_t)(w0 & 0xffffu)); acc = fma(x, x, acc);
+                x = bf16_half_to_f64((uint16_t)(w0 >> 16)); acc2 = fma(x, x, acc2);
+                x = bf16_half_to_f64((uint16_t)(w1 & 0xffffu)); acc = fma(x, x, acc);
+                x = bf16_half_to_f64((uint16_t)(w1 >> 16)); acc2 = fma(x, x, acc2);
+            } else if (kVar == 5) {
+                double x, y;
+                const uint32_t t0 = w0 & 0x7fff0000u, t1 = w1 & 0x7fff0000u;
+                mx = __vimax3_u32(mx, t0, t1);
+                x = bf16_half_to_f64((uint16_t)(w0 & 0xffffu)); acc = fma(x, x, acc);
+                y = bf16_bits_to_scaled_f64(__umulhi(t0, 1u << 29)); acc2 = fma(y, y, acc2);
+                x = bf16_half_to_f64((uint16_t)(w1 & 0xffffu)); acc = fma(x, x, acc);
+                y = bf16_bits_to_scaled_f64(__umulhi(t1, 1u << 29)); acc2 = fma(y, y, acc2);
             } else {
                 double x, y;
                 x = (double)__uint_as_float(w0 << 16); acc = fma(x, x, acc);
@@ -740,8 +762,8 @@ norm_pow2_bf16_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restr
         bad = ((mx & 0xffffu) >= 0x7f80u || (mx >> 16) >= 0x7f80u) ? 1 : 0;
         acc = acc * scale.hi + acc2 * scale.hi;
     } else {
-        bad = (kVar == 2 && mx >= 0x7f800000u) ? 1 : 0;
-        acc = acc * scale.lo + acc2 * (kVar == 2 ? scale.hi : scale.lo);
+        bad = ((kVar == 2 || kVar == 5) && mx >= 0x7f800000u) ? 1 : 0;
+        acc = acc * scale.lo + acc2 * ((kVar == 2 || kVar == 5) ? scale.hi : scale.lo);
     }
     bad |= (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN among the converted elements
     norm_finish(acc, bad, out, max_norm, finalize);

@@ -176,18 +176,11 @@ static std::vector<Piece> shard_pieces(const std::vector<uint64_t> &numel, const
                                        int rank, uint64_t shard)
 {
     std::vector<Piece> out;
-    const uint64_t begin = (uint64_t)rank * shard, end = begin + shard;
-    uint64_t off = 0;
-    for (size_t t = 0; t < numel.size(); ++t) {
-        uint64_t lo = off > begin ? off : begin;
-        uint64_t hi = off + numel[t] < end ? off + numel[t] : end;
-        if (hi > lo) {
-            Piece p;
-            p.tensor = t; p.offset = lo - off; p.n = hi - lo;
-            p.bucket_off = lo; p.state_off = lo - begin; p.group = group_of[t];
-            out.push_back(p);
-        }
-        off += numel[t];
+    for (const ShardRow &r : shard_rows(numel, group_of, rank, shard)) {
+        Piece p;
+        p.tensor = r.tensor; p.offset = r.offset; p.n = r.n;
+        p.bucket_off = r.bucket_off; p.state_off = r.bucket_off - (uint64_t)rank * shard; p.group = r.group;
+        out.push_back(p);
     }
     return out;
 }
@@ -471,7 +464,7 @@ static int32_t zero1_host_step_sharded(nbo_optimizer *h, Zero1 *z, void *const *
         std::vector<int32_t> row_group(np);
         for (size_t i = 0; i < np; ++i) {
             row_n[i] = rows[q][i].n;
-            row_head[i] = (uint32_t)((4 - (rows[q][i].bucket_off & 3)) & 3);  // as bind_flat sets it
+            row_head[i] = bucket_row_head(rows[q][i].bucket_off);  // as bind_flat sets it
             row_group[i] = rows[q][i].group;
         }
         plans[q] = plan_host_slices(row_n, row_head, row_group, (int32_t)h->groups.size(), slice_chunks);

@@ -61,6 +61,20 @@ def exchange_unique_id(rank: int, world: int, group=None) -> Optional[bytes]:
     return bytes(buf.tolist())
 
 
+class _RawDeviceMemory:
+    """Zero-copy handle on device memory the library allocated, for torch.as_tensor."""
+
+    def __init__(self, ptr: int, n_int16: int):
+        self.__cuda_array_interface__ = {"shape": (n_int16,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
+def _device_view(ptr: int, elems: int, device: int) -> torch.Tensor:
+    """A bf16 torch view of `elems` elements at device address `ptr` (memory owned by the library)."""
+    t = torch.as_tensor(_RawDeviceMemory(ptr, elems), device=torch.device("cuda", device))
+    assert t.data_ptr() == ptr
+    return t.view(torch.bfloat16)
+
+
 class Zero1AdamW:
     """Sharded mixed-precision Adam/AdamW on flat bf16 buckets."""
 
@@ -167,10 +181,76 @@ class Zero1AdamW:
         self._h.check(self._h.lib.nbo_zero1_attach_symmetric(
             self._h.h, C.c_void_p(gflat.data_ptr()), gp, gmc, C.c_void_p(pflat.data_ptr()), pp, pmc, transport))
         self._symm = (pflat, gflat, ph, gh)          # keep the mappings alive
+        self.peer_grad_ptrs = list(gh.buffer_ptrs)
         self.has_multicast = bool(gh.multicast_ptr and ph.multicast_ptr)
         torch.cuda.synchronize()
         dist.barrier(group)
         return pflat, gflat
+
+    def attach_symmetric_native(self, group=None, transport: int = 0, want_multicast: bool = True,
+                                timeout_s: float = 60.0):
+        """`attach_symmetric` without torch's symmetric-memory module: the two buckets are made by the
+        library itself (nbo_symm_alloc: CUDA virtual-memory allocations mapped into every rank, bound to an
+        NVSwitch multicast object where the fabric has one).  torch.distributed only carries the 16-byte
+        token from rank 0 to the others.  Returns (params_flat, grads_flat) as torch views of that memory;
+        call `release_symmetric()` on every rank before the process ends."""
+        import torch.distributed as dist
+        lib = self._h.lib
+        tok = torch.zeros(16, dtype=torch.uint8)
+        if self.rank == 0:
+            raw = (C.c_uint8 * 16)()
+            L.check(None, lib.nbo_symm_token(raw))
+            tok = torch.tensor(list(raw), dtype=torch.uint8)
+        if self.world > 1:
+            if dist.get_backend(group) == "nccl":
+                t = tok.to(torch.device("cuda", self._h.device))
+                dist.broadcast(t, src=0, group=group)
+                tok = t.cpu()
+            else:
+                dist.broadcast(tok, src=0, group=group)
+        token = (C.c_uint8 * 16)(*tok.tolist())
+        self._native_tag = getattr(Zero1AdamW, "_next_symm_tag", 0)
+        Zero1AdamW._next_symm_tag = self._native_tag + 2
+        handles, views, peers, mcs = [], [], [], []
+        for k in range(2):                                   # 0: params, 1: grads
+            sh = C.c_void_p()
+            L.check(None, lib.nbo_symm_alloc(self._h.device, self.rank, self.world, 2 * self.padded, token,
+                                             self._native_tag + k, 1 if want_multicast else 0, float(timeout_s),
+                                             C.byref(sh)))
+            handles.append(sh)
+            local, mc = C.c_void_p(), C.c_void_p()
+            pp = (C.c_void_p * self.world)()
+            L.check(None, lib.nbo_symm_pointers(sh, C.byref(local), pp, C.byref(mc)))
+            views.append(_device_view(local.value, self.padded, self._h.device))
+            peers.append(pp)
+            mcs.append(mc)
+        self._native = handles
+        (pflat, gflat), (pp, gp), (pmc, gmc) = views, peers, mcs
+        pflat.zero_(); gflat.zero_()
+        self._h.check(lib.nbo_zero1_attach_symmetric(
+            self._h.h, C.c_void_p(gflat.data_ptr()), gp, gmc if gmc.value else None,
+            C.c_void_p(pflat.data_ptr()), pp, pmc if pmc.value else None, transport))
+        self.has_multicast = bool(gmc.value and pmc.value)
+        self.peer_grad_ptrs = [gp[r] for r in range(self.world)]
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group)
+        return pflat, gflat
+
+    def release_symmetric(self, group=None) -> None:
+        """Frees the buckets made by `attach_symmetric_native` (unbinds them from the multicast object first).
+        Collective in effect: every rank calls it once no rank uses the buckets any more."""
+        handles = getattr(self, "_native", None)
+        if not handles:
+            return
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group)
+        self._h.close()                                      # the handle's tables point into the buckets
+        for sh in handles:
+            L.check(None, self._h.lib.nbo_symm_free(sh))
+        self._native = None
 
     def step_fused(self, *, average: bool = False, use_scaler: bool = False, max_norm: float = 0.0) -> StepOutcome:
         """One step on the attached buckets with reduce-scatter and all-gather fused into the kernels."""

@@ -112,6 +112,40 @@ static void check_plan(const std::vector<uint64_t> &row_n, const std::vector<uin
         CHECK(next_elem[r] == row_n[r], "row %zu covered to %llu of %llu", r, (unsigned long long)next_elem[r], (unsigned long long)row_n[r]);
 }
 
+// Sharded plans: every rank's slices together must copy every element of the bucket exactly once, each slice's
+// ranges must lie inside the rank's shard, and all ranks must be able to agree on the number of slices.
+static void check_sharded(const std::vector<uint64_t> &numel, const std::vector<int32_t> &group_of, int32_t ngroups,
+                          int world, uint64_t slice_chunks)
+{
+    uint64_t total = 0;
+    for (uint64_t n : numel) total += n;
+    uint64_t shard = (total + world - 1) / world;
+    shard = (shard + 7) & ~7ull;
+    if (shard == 0) shard = 8;
+    std::vector<int> covered(total, 0);
+    for (int q = 0; q < world; ++q) {
+        std::vector<ShardRow> rows = shard_rows(numel, group_of, q, shard);
+        std::vector<uint64_t> row_n;
+        std::vector<uint32_t> row_head;
+        std::vector<int32_t> row_group;
+        uint64_t owned = 0;
+        for (const ShardRow &r : rows) {
+            CHECK(r.bucket_off >= (uint64_t)q * shard && r.bucket_off + r.n <= (uint64_t)(q + 1) * shard, "row outside its shard");
+            row_n.push_back(r.n); row_head.push_back(bucket_row_head(r.bucket_off)); row_group.push_back(r.group);
+            owned += r.n;
+        }
+        uint64_t want = total > (uint64_t)q * shard ? total - (uint64_t)q * shard : 0;
+        if (want > shard) want = shard;
+        CHECK(owned == want, "rank %d owns %llu of %llu elements", q, (unsigned long long)owned, (unsigned long long)want);
+        check_plan(row_n, row_head, row_group, ngroups, slice_chunks);
+        HostPlan plan = plan_host_slices(row_n, row_head, row_group, ngroups, slice_chunks);
+        for (const SliceCopy &c : plan.copies)
+            for (uint64_t e = rows[c.row].bucket_off + c.lo; e < rows[c.row].bucket_off + c.hi; ++e) covered[e] += 1;
+    }
+    for (uint64_t e = 0; e < total; ++e)
+        if (covered[e] != 1) { CHECK(false, "bucket element %llu copied %d times (world %d)", (unsigned long long)e, covered[e], world); break; }
+}
+
 int main()
 {
     std::mt19937_64 rng(1234);
@@ -136,6 +170,18 @@ int main()
         uint64_t slice_chunks = 1 + rng() % 9;
         if (t % 7 == 0) slice_chunks = 1u << 20;
         check_plan(n, hd, gr, ngroups, slice_chunks);
+    }
+    for (int t = 0; t < 200; ++t) {
+        int tensors = 1 + (int)(rng() % 10);
+        int32_t ngroups = 1 + (int32_t)(rng() % 3);
+        std::vector<uint64_t> n(tensors);
+        std::vector<int32_t> gr(tensors);
+        for (int r = 0; r < tensors; ++r) {
+            n[r] = (rng() % 5 == 0) ? rng() % 6 : rng() % 50000;
+            gr[r] = (int32_t)(rng() % ngroups);
+        }
+        const int worlds[] = {1, 2, 3, 4, 8};
+        check_sharded(n, gr, ngroups, worlds[rng() % 5], 1 + rng() % 6);
     }
     if (g_fail) { printf("HOST_PLAN_FAILED %d\n", g_fail); return 1; }
     printf("HOST_PLAN_OK\n");

@@ -52,7 +52,7 @@ def rust_functions():
 
 
 C_TO_RUST = {"int32_t": "i32", "uint32_t": "u32", "uint64_t": "u64", "double": "f64", "float": "f32", "uint8_t": "u8",
-             "char": "c_char", "void": "c_void", "nbo_optimizer": "NboOptimizer", "nbo_group_config": "NboGroupConfig",
+             "char": "c_char", "void": "c_void", "nbo_optimizer": "NboOptimizer", "nbo_symm": "NboSymm", "nbo_group_config": "NboGroupConfig",
              "nbo_scaler_state": "NboScalerState", "nbo_lr_schedule": "NboLrSchedule", "nbo_step_result": "NboStepResult"}
 
 

@@ -70,13 +70,14 @@ def test_bucket_validation(nb):
         nb.Zero1AdamW.adamw(1e-3, 0.0, [(100,)], 2, 2)
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer", "mcast"])
+@pytest.mark.parametrize("mode", ["nccl", "peer", "mcast", "native-peer", "native-mcast"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_multi_gpu_matches_single_gpu(world, mode):
-    """nccl: collectives around the update; peer / mcast: collectives fused into the kernels."""
+    """nccl: collectives around the update; peer / mcast: collectives fused into the kernels; native-*: the same
+    on buckets the library allocates itself (no framework symmetric memory)."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    port = 29500 + world + {"nccl": 0, "peer": 20, "mcast": 40}[mode]
+    port = 29500 + world + {"nccl": 0, "peer": 20, "mcast": 40, "native-peer": 60, "native-mcast": 80}[mode]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "zero1_worker.py"), mode]

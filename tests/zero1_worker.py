@@ -1,10 +1,12 @@
 """One rank of the multi-GPU ZeRO-1 check (launched by tests/test_gpu_zero1.py under torch.distributed.run).
 
-    zero1_worker.py [nccl|peer|mcast]
+    zero1_worker.py [nccl|peer|mcast|native-peer|native-mcast]
 
 nccl  : reduce-scatter / all-gather issued as NCCL collectives around the local update (nbo_zero1_step)
 peer  : collectives fused into the kernels with plain peer loads/stores (nbo_zero1_step_fused, transport 1)
 mcast : the same through NVSwitch multimem ld_reduce / st (transport 2)
+native-peer / native-mcast : as peer / mcast, with the symmetric buckets made by the library itself
+        (nbo_symm_alloc: CUDA virtual memory + multicast object) instead of torch's symmetric-memory module
 
 Every rank holds its own bf16 gradients.  Each sharded step is checked three ways:
   (0) the cross-rank reduction against an independent reference: every rank's INPUT gradients are
@@ -91,8 +93,15 @@ def main():
         pflat = torch.zeros(padded, dtype=torch.bfloat16, device="cuda")
         gbuf = None
     else:
-        pflat, gbuf = z.attach_symmetric(transport=1 if mode == "peer" else 2)
+        native = mode.startswith("native-")               # buckets made by the library's own nbo_symm_alloc
+        if native:
+            mode = mode[len("native-"):]
+            pflat, gbuf = z.attach_symmetric_native(transport=1 if mode == "peer" else 2)
+        else:
+            pflat, gbuf = z.attach_symmetric(transport=1 if mode == "peer" else 2)
         if mode == "mcast" and not z.has_multicast:
+            if native:
+                z.release_symmetric()
             if rank == 0:
                 print("ZERO1_WORKER_SKIP no multicast mapping on this fabric")
             dist.destroy_process_group()
@@ -167,8 +176,12 @@ def main():
     dist.all_gather(digests, digest)
     assert all(int(d) == int(digest) for d in digests)
     dist.barrier()
+    if sys.argv[1:] and sys.argv[1].startswith("native-"):
+        assert "torch.distributed._symmetric_memory" not in sys.modules     # the framework module was never needed
+        del pflat, gbuf, gflat, before
+        z.release_symmetric()                               # unbind / unmap on every rank before anyone exits
     if rank == 0:
-        print("ZERO1_WORKER_OK", world, mode)
+        print("ZERO1_WORKER_OK", world, sys.argv[1] if sys.argv[1:] else mode)
     dist.destroy_process_group()
 
 
