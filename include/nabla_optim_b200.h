@@ -440,6 +440,17 @@ NBO_API int32_t nbo_symm_free(nbo_symm *s);
 NBO_API int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scaler,
                                      double max_norm, nbo_step_result *result);
 
+/* nbo_zero1_step_fused without any host wait, the sharded counterpart of nbo_step_mixed_async: step
+ * counters, bias corrections and the GradScaler bookkeeping advance in the handle's device-resident state,
+ * every launch has constant arguments, and the skip decision (trainer.rs:230-237) is taken and accounted
+ * for on the device from the all-gathered per-rank sums, identically on every rank.  The call returns as
+ * soon as the work is enqueued, so the caller can go on to its next backward pass.
+ * nbo_step_mixed_collect hands the state back and reports the last outcome; on a sharded handle its wait is
+ * bounded by nbo_zero1_set_timeout, which is where a rank that stopped taking part is noticed.
+ * Arithmetic and results are those of nbo_zero1_step_fused. */
+NBO_API int32_t nbo_zero1_step_fused_async(nbo_optimizer *h, int32_t average, int32_t use_scaler,
+                                           double max_norm);
+
 /* Whether the fused step also writes the reduced gradient into this rank's
  * slice of its own gradient bucket (default 1, what an in-place reduce-scatter
  * leaves behind; nabla-train/src/dist.rs:36-43 hands the mean back to the

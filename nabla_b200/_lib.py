@@ -99,6 +99,7 @@ SIGNATURES = {
                                    C.POINTER(StepResult)]),
     "nbo_zero1_step_host": (C.c_int32, [_H, C.c_void_p, C.c_void_p, C.c_uint64, _PP, _PP, C.c_uint64, C.c_int32,
                                         C.c_int32, C.c_double, C.POINTER(StepResult)]),
+    "nbo_zero1_step_fused_async": (C.c_int32, [_H, C.c_int32, C.c_int32, C.c_double]),
     "nbo_zero1_keep_reduced_grads": (C.c_int32, [_H, C.c_int32]),
     "nbo_symm_token": (C.c_int32, [C.c_void_p]),
     "nbo_symm_alloc": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_uint64, C.c_void_p, C.c_int32, C.c_int32,

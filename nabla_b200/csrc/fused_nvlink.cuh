@@ -219,6 +219,7 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
     uint2 *ring = reinterpret_cast<uint2 *>(ring_raw);  // [stage][remote slot][kChunkItems]
     if (!barrier_passed(pa))
         return;
+    if (pa.hp_dev != nullptr) hp = *pa.hp_dev;
     float clip = 1.0f;
     if (ctrl != nullptr) {
         if (ctrl->skip)
@@ -351,6 +352,7 @@ zero1_reduce_norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__re
 {
     double acc = 0.0;
     int bad = 0;
+    if (pa.inv_scale_dev != nullptr) inv_scale = *pa.inv_scale_dev;
     const bool go = barrier_passed(pa);  // a failed barrier leaves every rank's memory alone; the partials still add up
     for (uint32_t c = blockIdx.x; go && c < nchunks; c += gridDim.x) {
         const Chunk ck = chunks[c];

@@ -153,6 +153,10 @@ int32_t launch_prepare(nbo_optimizer *h, int use_scaler);
 int32_t launch_commit(nbo_optimizer *h, bool checked, int use_scaler);
 int32_t launch_adam_mixed_dev(nbo_optimizer *h, uint32_t chunk_begin, uint32_t nchunks, int group, bool with_ctrl);
 
+int32_t push_dev_state(nbo_optimizer *h);
+// Sharded handles: waits for the handle's stream with the nbo_zero1_set_timeout limit (zero1.cu).
+int32_t zero1_bounded_wait(nbo_optimizer *h, const char *what);
+
 // Brings the host mirrors up to date after asynchronous steps (synchronises the stream); no-op otherwise.
 int32_t collect_dev_state(nbo_optimizer *h);
 

@@ -281,6 +281,23 @@ int32_t collect_dev_state(nbo_optimizer *h)
     return NBO_OK;
 }
 
+// Sends the host-side optimizer / scaler state to its device copy when the host holds the newer one
+// (stream-ordered); the asynchronous steps then advance the device copy.
+int32_t push_dev_state(nbo_optimizer *h)
+{
+    if (h->dev_newer) return NBO_OK;
+    DevState &st = *h->h_state;
+    st.scale = h->scaler.scale; st.growth_factor = h->scaler.growth_factor;
+    st.backoff_factor = h->scaler.backoff_factor; st.growth_interval = h->scaler.growth_interval;
+    st.consecutive_ok = h->scaler.consecutive_ok; st.ngroups = (int32_t)h->groups.size();
+    for (size_t g = 0; g < h->groups.size(); ++g) {
+        const nbo_group_config &c = h->groups[g].cfg;
+        st.g[g] = DevGroup{c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.kind, 0, h->groups[g].step_count};
+    }
+    NBO_CUDA(h, cudaMemcpyAsync(h->d_state, h->h_state, sizeof(DevState), cudaMemcpyHostToDevice, h->stream));
+    return NBO_OK;
+}
+
 static bool valid_kind(int32_t k) { return k == NBO_ADAMW || k == NBO_ADAM || k == NBO_SGD; }
 
 }  // namespace nbo
@@ -759,17 +776,8 @@ int32_t nbo_step_mixed_async(nbo_optimizer *h, uint64_t n, void *const *params_b
     DeviceGuard guard(h->device);
     int32_t rc = bind_list(h, n, params_bf16, grads_bf16, 2, "step");
     if (rc != NBO_OK) return rc;
-    if (!h->dev_newer) {  // the host holds the current state: send it down (stream-ordered)
-        DevState &st = *h->h_state;
-        st.scale = h->scaler.scale; st.growth_factor = h->scaler.growth_factor;
-        st.backoff_factor = h->scaler.backoff_factor; st.growth_interval = h->scaler.growth_interval;
-        st.consecutive_ok = h->scaler.consecutive_ok; st.ngroups = (int32_t)h->groups.size();
-        for (size_t g = 0; g < h->groups.size(); ++g) {
-            const nbo_group_config &c = h->groups[g].cfg;
-            st.g[g] = DevGroup{c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.kind, 0, h->groups[g].step_count};
-        }
-        NBO_CUDA(h, cudaMemcpyAsync(h->d_state, h->h_state, sizeof(DevState), cudaMemcpyHostToDevice, h->stream));
-    }
+    rc = push_dev_state(h);
+    if (rc != NBO_OK) return rc;
     bool checked = use_scaler || max_norm > 0.0;
     rc = launch_prepare(h, use_scaler);
     if (rc != NBO_OK) return rc;
@@ -796,7 +804,9 @@ int32_t nbo_step_mixed_collect(nbo_optimizer *h, nbo_step_result *result, uint64
     if (!h->dev_newer && h->h_state->ngroups == 0)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: no asynchronous step has been enqueued");
     DeviceGuard guard(h->device);
-    int32_t rc = collect_dev_state(h);
+    int32_t rc = h->zero1 ? zero1_bounded_wait(h, "the asynchronous sharded steps") : NBO_OK;
+    if (rc != NBO_OK) return rc;
+    rc = collect_dev_state(h);
     if (rc != NBO_OK) return rc;
     const DevState &st = *h->h_state;
     if (result) {

@@ -131,6 +131,8 @@ struct PeerArgs {
     int32_t keep_reduced; // also write the reduced gradient into this rank's slice of its own bucket
     int32_t barrier_expect;        // value *barrier_seen must hold for the kernel to touch any peer memory
     const int32_t *barrier_seen;   // output of the stream-ordered cross-rank barrier that precedes the kernel
+    const AdamHP *hp_dev;          // asynchronous step: this launch's hyper-parameters, written by prepare_kernel
+    const float *inv_scale_dev;    // asynchronous step: f32(1 / loss scale) on the device
     int64_t g_mc, p_mc;   // delta to the NVSwitch multicast mapping of the bucket (0 = none)
     int64_t g_peer[kMaxPeers];
     int64_t p_peer[kMaxPeers];

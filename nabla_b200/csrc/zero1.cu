@@ -185,6 +185,8 @@ static std::vector<Piece> shard_pieces(const std::vector<uint64_t> &numel, const
     return out;
 }
 
+int32_t zero1_bounded_wait(nbo_optimizer *h, const char *what) { return stream_wait(h, h->zero1, what); }
+
 void zero1_destroy(nbo_optimizer *h)
 {
     if (!h->zero1) return;
@@ -331,6 +333,7 @@ int32_t nbo_zero1_init_master(nbo_optimizer *h, const void *params_flat_bf16)
 int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, int32_t average,
                        int32_t use_scaler, double max_norm, nbo_step_result *result)
 {
+    NBO_SYNC_STATE(h);
     if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
     if (!params_flat || !grads_flat) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
     Zero1 *z = h->zero1;
@@ -382,13 +385,23 @@ int32_t nbo_zero1_step(nbo_optimizer *h, void *params_flat, void *grads_flat, in
 
 // Enqueues one fused sharded step on the attached buckets, up to and including the closing barrier and the
 // copy of the decision record; nothing here waits on the host.
-static int32_t enqueue_fused_step(nbo_optimizer *h, Zero1 *z, int32_t average, int32_t use_scaler, double max_norm)
+// dev_state: the asynchronous form - hyper-parameters, loss scale and step counters are read from and advanced
+// in the handle's device-resident state (prepare_kernel / commit_kernel), nothing is read back.
+static int32_t enqueue_fused_step(nbo_optimizer *h, Zero1 *z, int32_t average, int32_t use_scaler, double max_norm,
+                                  bool dev_state = false)
 {
     NcclApi *a = nccl_api();
     PeerArgs pa = z->pa;
     pa.average = average ? 1 : 0;
     pa.keep_reduced = z->keep_reduced ? 1 : 0;
     pa.barrier_seen = z->d_barrier + 1;
+    if (dev_state) {
+        int32_t r0 = push_dev_state(h);
+        if (r0 != NBO_OK) return r0;
+        r0 = launch_prepare(h, use_scaler);
+        if (r0 != NBO_OK) return r0;
+        pa.inv_scale_dev = h->d_inv_scale;
+    }
 
     // every rank's gradients are final, and nobody still reads the old params, before any peer access
     int32_t rc = enqueue_barrier(h, z, &pa.barrier_expect);
@@ -413,6 +426,7 @@ static int32_t enqueue_fused_step(nbo_optimizer *h, Zero1 *z, int32_t average, i
         uint32_t nc = g.chunk_end - g.chunk_begin;
         if (nc == 0) continue;
         AdamHP hp = adam_hparams(g.cfg, g.step_count + 1, inv_scale);
+        if (dev_state) pa.hp_dev = h->d_hp + (&g - h->groups.data());
         rc = launch_zero1_fused_update(h, g.chunk_begin, nc, hp, checked, pa, in_transport, z->transport);
         if (rc != NBO_OK) return rc;
     }
@@ -420,11 +434,20 @@ static int32_t enqueue_fused_step(nbo_optimizer *h, Zero1 *z, int32_t average, i
     // every rank's parameter stores have landed everywhere before anyone uses the params
     rc = enqueue_barrier(h, z, nullptr);
     if (rc != NBO_OK) return rc;
+    if (dev_state) {
+        rc = launch_commit(h, checked, use_scaler);
+        if (rc != NBO_OK) return rc;
+        h->dev_newer = true;
+        h->last_async_checked = checked;
+        return NBO_OK;
+    }
     if (checked)
         NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost,
                                     h->stream));
     return NBO_OK;
 }
+
+
 
 // Host-streamed sharded step, world > 1, on the attached symmetric buckets.
 //
@@ -571,6 +594,7 @@ int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, void *grads
                             void *const *params_host, const void *const *grads_host, uint64_t slice_elems,
                             int32_t average, int32_t use_scaler, double max_norm, nbo_step_result *result)
 {
+    NBO_SYNC_STATE(h);
     if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
     Zero1 *z = h->zero1;
     if (!params_flat_dev || !grads_flat_dev) return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: null bucket");
@@ -649,7 +673,9 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
     if (z->broken) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
     cudaError_t ce = cudaSetDevice(h->device);
     if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
-    int32_t rc = bind_flat(h, z->p_local, z->g_local);
+    int32_t rc = h->dev_newer ? collect_dev_state(h) : NBO_OK;  // asynchronous steps came before: take their state over
+    if (rc != NBO_OK) return rc;
+    rc = bind_flat(h, z->p_local, z->g_local);
     if (rc != NBO_OK) return rc;
     // Everything is stream-ordered behind the opening barrier; the kernels that touch other ranks' memory
     // check on the device that the barrier really completed, so the host waits once, at the end.
@@ -659,6 +685,22 @@ int32_t nbo_zero1_step_fused(nbo_optimizer *h, int32_t average, int32_t use_scal
     if (rc != NBO_OK) return rc;
     commit_step(h, use_scaler || max_norm > 0.0, use_scaler != 0, result);
     return NBO_OK;
+}
+
+int32_t nbo_zero1_step_fused_async(nbo_optimizer *h, int32_t average, int32_t use_scaler, double max_norm)
+{
+    if (!h || !h->zero1) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: not a ZeRO-1 handle");
+    Zero1 *z = h->zero1;
+    if (!z->attached)
+        return fail(h, NBO_ERR_STATE, "nabla-optim-b200: nbo_zero1_step_fused_async before nbo_zero1_attach_symmetric");
+    if (z->broken) return fail(h, NBO_ERR_STATE, "nabla-optim-b200: the communicator was aborted; create a new handle");
+    if (h->groups.size() > (size_t)kMaxDevGroups)
+        return fail(h, NBO_ERR_INVALID, "nabla-optim-b200: the asynchronous step supports at most 32 groups");
+    cudaError_t ce = cudaSetDevice(h->device);
+    if (ce != cudaSuccess) return fail_cuda(h, ce, "cudaSetDevice");
+    int32_t rc = bind_flat(h, z->p_local, z->g_local);
+    if (rc != NBO_OK) return rc;
+    return enqueue_fused_step(h, z, average, use_scaler, max_norm, true);
 }
 
 int32_t nbo_zero1_keep_reduced_grads(nbo_optimizer *h, int32_t on)

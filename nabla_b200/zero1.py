@@ -259,6 +259,17 @@ class Zero1AdamW:
                                                        float(max_norm), C.byref(res)))
         return StepOutcome.from_c(res)
 
+    def step_fused_async(self, *, average: bool = False, use_scaler: bool = False, max_norm: float = 0.0) -> None:
+        """Enqueues one fused sharded step and returns without waiting; `collect()` hands the state back."""
+        self._h.check(self._h.lib.nbo_zero1_step_fused_async(self._h.h, 1 if average else 0, 1 if use_scaler else 0,
+                                                             float(max_norm)))
+
+    def collect(self):
+        """(outcome of the most recent asynchronous step, asynchronous steps completed on the device)."""
+        res, k = L.StepResult(), C.c_uint64()
+        self._h.check(self._h.lib.nbo_step_mixed_collect(self._h.h, C.byref(res), C.byref(k)))
+        return StepOutcome.from_c(res), k.value
+
     def state_shard(self, which: int) -> torch.Tensor:
         """fp32 state of this rank's shard on the host: 0 = m, 1 = v, 2 = master."""
         out = torch.empty(self.shard, dtype=torch.float32)

@@ -101,6 +101,41 @@ def main():
         assert torch.equal(ph[:total].view(torch.int16), pf[:total].view(torch.int16)), (rank, step)
     for which in (0, 1, 2):
         assert torch.equal(zf.state_shard(which), zh.state_shard(which)), f"state {which} differs"
+
+    # the asynchronous fused step (state advanced on the device, no host wait) against the synchronous one:
+    # four steps enqueued back to back, the second of them skipped because of an inf, then one collect
+    scale = zf.scaler_state().scale
+    assert scale == zh.scaler_state().scale
+    seq = []
+    for k in range(4):
+        g = torch.zeros(zf.padded, dtype=torch.bfloat16, device="cuda")
+        g[:total] = (torch.randn(total, device="cuda", generator=gr) * 1e-4 * scale).to(torch.bfloat16)
+        if k == 1 and rank == 0:
+            g[total - 3] = float("nan")
+        seq.append(g)
+    outcomes = []
+    for g in seq:
+        gf.copy_(g)
+        torch.cuda.synchronize(); dist.barrier()
+        outcomes.append(zf.step_fused(average=True, use_scaler=True, max_norm=1e-3))
+    stage = [torch.empty_like(gh) for _ in seq]                 # the asynchronous side must not wait between steps:
+    for s_, g in zip(stage, seq):                               # every step's gradients are staged up front
+        s_.copy_(g)
+    torch.cuda.synchronize(); dist.barrier()
+    for s_ in stage:
+        gh.copy_(s_, non_blocking=True)                          # stream-ordered before the step that reads it
+        zh.step_fused_async(average=True, use_scaler=True, max_norm=1e-3)
+    last, done = zh.collect()
+    assert done == len(seq)
+    assert [o.applied for o in outcomes] == [True, False, True, True]
+    assert (last.applied, last.loss_scale, last.step_count, last.grad_norm) == \
+           (outcomes[-1].applied, outcomes[-1].loss_scale, outcomes[-1].step_count, outcomes[-1].grad_norm)
+    assert torch.equal(ph[:total].view(torch.int16), pf[:total].view(torch.int16)), "async params differ"
+    for which in (0, 1, 2):
+        assert torch.equal(zf.state_shard(which), zh.state_shard(which)), f"async state {which} differs"
+    sa, sb = zf.scaler_state(), zh.scaler_state()
+    assert (sa.scale, sa.consecutive_ok) == (sb.scale, sb.consecutive_ok)
+    assert zf.step_count(0) == zh.step_count(0) and zf.step_count(1) == zh.step_count(1)
     dist.barrier()
     if rank == 0:
         print("ZERO1_HOST_OK", world, mode)
