@@ -88,18 +88,14 @@ int32_t launch_adam_mixed(nbo_optimizer *h, uint32_t cb, uint32_t nc, const Adam
                 : launch_adam_mixed_one<false, false>(h, cb, nc, hp, nullptr, nullptr);
 }
 
-#ifndef NBO_NORM_CTAS_PER_SM
-#define NBO_NORM_CTAS_PER_SM 4
-#endif
-
 // Every norm launch of a handle uses the same grid whichever kernel variant runs (generic, per-element flag,
-// power-of-two scale): the per-thread accumulation order and the order of the per-CTA partials depend on the
+// power-of-two scale) of the same element type: the per-thread accumulation order and the order of the per-CTA partials depend on the
 // grid alone, so the synchronous and the asynchronous step, and a step before and after the loss scale leaves
 // the power-of-two fast path, produce the same f64 sum for the same gradients.
-static int norm_grid(const nbo_optimizer *h)
+static int norm_grid(const nbo_optimizer *h, bool bf16)
 {
     uint32_t units = (h->nchunks + kNormBatch - 1) / kNormBatch;  // one loop iteration takes kNormBatch chunks
-    long long g = (long long)h->sm_count * NBO_NORM_CTAS_PER_SM;
+    long long g = (long long)h->sm_count * (bf16 ? kNormCtasPerSm : kNormCtasPerSmF32);
     if (g > h->max_grid) g = h->max_grid;
     if (g > (long long)units) g = units;
     return (int)(g < 1 ? 1 : g);
@@ -109,14 +105,10 @@ template <bool kBf16, bool kCheckEach>
 static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, int finalize, const NormOut &out,
                             const float *inv_scale_dev = nullptr)
 {
-    int grid = norm_grid(h);
+    int grid = norm_grid(h, kBf16);
     norm_kernel<kBf16, kCheckEach><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
                                                                   inv_scale, max_norm, finalize, out, inv_scale_dev);
 }
-
-#ifndef NBO_NORM_VARIANT
-#define NBO_NORM_VARIANT 2  // 0 = always the generic kernel; 1..3 = norm_pow2_bf16_kernel<kVar> where it applies
-#endif
 
 // k with inv_scale == 2^-k exactly and 0 <= k <= 16 (the range in which the f32 product g * 2^-k is exact for
 // every finite bf16 g, so that the scale may be applied to the sum instead of to each element); -1 otherwise.
@@ -131,13 +123,11 @@ static int pow2_unscale_exponent(float inv_scale)
 int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize)
 {
     NormOut out{h->d_partial_sum, h->d_partial_bad, h->d_ticket, h->d_local, h->d_ctrl};
-    const int k = (bf16 && NBO_NORM_VARIANT != 0) ? pow2_unscale_exponent(inv_scale) : -1;
+    const int k = bf16 ? pow2_unscale_exponent(inv_scale) : -1;
     if (k >= 0) {
-        constexpr int kVar = NBO_NORM_VARIANT == 0 ? 2 : NBO_NORM_VARIANT;
-        Pow2Scale sc{ldexp(1.0, -2 * k), ldexp(1.0, -2 * k - 208)};
-        int grid = norm_grid(h);
-        norm_pow2_bf16_kernel<kVar><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, sc, max_norm,
-                                                                   finalize, out);
+        int grid = norm_grid(h, true);
+        norm_pow2_bf16_kernel<<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, ldexp(1.0, -2 * k),
+                                                            max_norm, finalize, out);
         return launched(h);
     }
     // the flag can be read off the sum only while the unscale factor cannot overflow a finite gradient

@@ -516,11 +516,15 @@ __device__ __forceinline__ void sq_acc_fast(float g, float inv_scale, double &ac
 // dependent loads (chunk entry -> table row) before the gradient loads can go
 // out; with 8 KiB of bf16 per chunk that chain, not HBM, bounded the kernel.
 // Taking kNormBatch chunks per iteration keeps 4x the bytes in flight per chain.
+// Resident CTAs per SM every norm kernel is compiled for and launched with (5 x 256 threads at <= 48
+// registers); the power-of-two kernel measured 5.88 / 6.09 / 5.69 TB/s at 4 / 5 / 8 CTAs per SM.
+constexpr int kNormCtasPerSm = 5;
+constexpr int kNormCtasPerSmF32 = 4;  // fp32 gradients: 16 x 128-bit loads per thread are in flight, 64 registers
 constexpr int kNormBatch = 4;  // 2 and 8 measured slower (4.4 / 4.1 vs 5.3 TB/s on 1.5 G bf16 elements)
 
 // kCheckEach = false: flag read off the sum (needs inv_scale <= 1); true: per-element test.
 template <bool kBf16, bool kCheckEach>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, kBf16 ? kNormCtasPerSm : kNormCtasPerSmF32)
 norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
             uint32_t nchunks, float inv_scale, double max_norm, int finalize, NormOut out,
             const float *__restrict__ inv_scale_dev)
@@ -610,39 +614,22 @@ norm_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chun
 }
 
 // ---- bf16 norm pass for power-of-two unscale factors ------------------------------------------------
-// The generic kernel above spends one f32 multiply and one f32 -> f64 convert per element; the convert
-// runs on the quarter-rate conversion pipe and is what holds that kernel below the HBM roofline on bf16
-// input (2 bytes per element).  A loss scale is a power of two in practice (it starts at 2^16 and only
-// ever doubles or halves), and without a scaler the factor is 1, so here the factor 2^-k never touches an
-// element: squares of the raw values are accumulated and the exact power 2^-2k is applied once per
-// thread at the end.  For k <= 16 the reference's f32 product g * 2^-k is exact for every finite bf16 g
-// (the smallest bf16 subnormal, 2^-133, times 2^-16 is the smallest f32 subnormal), and scaling by a power
-// of two commutes with every rounding of the f64 accumulation (nothing under- or overflows: partial
-// sums stay within 2^-300 .. 2^500), so the sum has the same bits as the generic kernel's.
-//
-// The low half of each 32-bit word still goes through the convert; the high half is turned into an f64
-// with integer and FP64-pipe instructions only, which halves the load on the conversion pipe:
-//   bits = (w & 0x7fff0000) >> 3   placed in the high word of an f64 (low word zero) is |g| * 2^-896
-//          exactly, for normal, subnormal and zero g alike - bf16 and f64 share sign/exponent/mantissa
-//          order and the 3-bit shift moves the 8-bit exponent into the 11-bit field;
-//   y    = that * 2^1000           one exact FP64 multiply brings it back into the normal range
-//   acc2 = fma(y, y, acc2)         accumulates g^2 * 2^208, undone by the final scaling.
-// An inf/NaN in a high half is an ordinary finite number after this construction, so those are caught by
-// a running integer maximum of the masked words (one 3-input max per two words); low halves show in the
-// sum as before.  Accumulation order (low halves into `acc`, high halves into `acc2`) is the generic
-// kernel's.  kVar selects how many halves use the integer construction: 1 = none (convert only, scale
-// folded), 2 = high halves, 3 = both.
-struct Pow2Scale {
-    double lo;  // 2^-2k          applied to the chain of converted elements
-    double hi;  // 2^(-2k - 208)  applied to the chain of integer-built elements
-};
-
-__device__ __forceinline__ double bf16_bits_to_scaled_f64(uint32_t hi_word)
-{
-    return __hiloint2double((int)hi_word, 0) * 0x1p1000;
-}
-
-// bf16 -> f64 in one conversion instruction (exact for every input, inf / NaN included).
+// The generic kernel above spends a shift or mask, an f32 multiply, an f32 -> f64 convert and an f64 FMA per
+// element, and on bf16 input (2 bytes per element) that instruction stream, not HBM, is what bounds it.
+// A loss scale is a power of two in practice (it starts at 2^16 and only ever doubles or halves), and
+// without a scaler the factor is 1, so here the factor 2^-k never touches an element: the raw values are
+// squared and the exact power 2^-2k is applied once per thread at the end.  For k <= 16 the reference's
+// f32 product g * 2^-k is exact for every finite bf16 g (the smallest bf16 subnormal, 2^-133, times 2^-16 is
+// the smallest f32 subnormal), and scaling by a power of two commutes with every rounding of the f64
+// accumulation (nothing under- or overflows: partial sums stay within 2^-300 .. 2^300), so the sum has the
+// same bits as the generic kernel's.  Each bf16 half goes to f64 with ONE conversion instruction
+// (cvt.f64.bf16, exact for every input; inf / NaN stay inf / NaN and show in the sum), which leaves two
+// instructions per element.  Measured on 1.2 G elements: generic 4.81 TB/s; scale folded but shift + f32 ->
+// f64 convert kept 5.74; this form 6.09 (5 CTAs per SM).  Building the f64 by integer bit placement
+// instead of converting (mask, shift, one FP64 multiply to renormalise, integer max for inf / NaN) was also
+// built and measured: 4.9 TB/s for every element, 5.6 for every second one - more issue slots than the
+// convert it saves.  Accumulation order (low halves into `acc`, high halves into `acc2`) is the generic
+// kernel's.
 __device__ __forceinline__ double bf16_half_to_f64(uint16_t h)
 {
     double x;
@@ -650,9 +637,9 @@ __device__ __forceinline__ double bf16_half_to_f64(uint16_t h)
     return x;
 }
 
-template <int kVar, bool kFull>
+template <bool kFull>
 __device__ __forceinline__ void norm_pow2_batch(const char *const (&base)[kNormBatch], const uint32_t (&nitems)[kNormBatch],
-                                                double &acc, double &acc2, uint32_t &mx)
+                                                double &acc, double &acc2)
 {
     uint2 g[kNormBatch][kItemsPerThread];
 #pragma unroll
@@ -668,53 +655,20 @@ __device__ __forceinline__ void norm_pow2_batch(const char *const (&base)[kNormB
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             const uint32_t w0 = g[j][u].x, w1 = g[j][u].y;
-            if (kVar == 3) {
-                const uint32_t a0 = w0 & 0x7fff7fffu, a1 = w1 & 0x7fff7fffu;
-                mx = __vimax3_u16x2(mx, a0, a1);
-                double y;
-                y = bf16_bits_to_scaled_f64((a0 & 0xffffu) << 13); acc = fma(y, y, acc);
-                y = bf16_bits_to_scaled_f64(__umulhi(a0 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
-                y = bf16_bits_to_scaled_f64((a1 & 0xffffu) << 13); acc = fma(y, y, acc);
-                y = bf16_bits_to_scaled_f64(__umulhi(a1 & 0xffff0000u, 1u << 29)); acc2 = fma(y, y, acc2);
-            } else if (kVar == 4) {
-                double x;
-                x = bf16_half_to_f64((uint16_t)(w0 & 0xffffu)); acc = fma(x, x, acc);
-                x = bf16_half_to_f64((uint16_t)(w0 >> 16)); acc2 = fma(x, x, acc2);
-                x = bf16_half_to_f64((uint16_t)(w1 & 0xffffu)); acc = fma(x, x, acc);
-                x = bf16_half_to_f64((uint16_t)(w1 >> 16)); acc2 = fma(x, x, acc2);
-            } else if (kVar == 5) {
-                double x, y;
-                const uint32_t t0 = w0 & 0x7fff0000u, t1 = w1 & 0x7fff0000u;
-                mx = __vimax3_u32(mx, t0, t1);
-                x = bf16_half_to_f64((uint16_t)(w0 & 0xffffu)); acc = fma(x, x, acc);
-                y = bf16_bits_to_scaled_f64(__umulhi(t0, 1u << 29)); acc2 = fma(y, y, acc2);
-                x = bf16_half_to_f64((uint16_t)(w1 & 0xffffu)); acc = fma(x, x, acc);
-                y = bf16_bits_to_scaled_f64(__umulhi(t1, 1u << 29)); acc2 = fma(y, y, acc2);
-            } else {
-                double x, y;
-                x = (double)__uint_as_float(w0 << 16); acc = fma(x, x, acc);
-                if (kVar == 2) {
-                    const uint32_t t0 = w0 & 0x7fff0000u, t1 = w1 & 0x7fff0000u;
-                    mx = __vimax3_u32(mx, t0, t1);
-                    y = bf16_bits_to_scaled_f64(__umulhi(t0, 1u << 29)); acc2 = fma(y, y, acc2);
-                    x = (double)__uint_as_float(w1 << 16); acc = fma(x, x, acc);
-                    y = bf16_bits_to_scaled_f64(__umulhi(t1, 1u << 29)); acc2 = fma(y, y, acc2);
-                } else {
-                    x = (double)__uint_as_float(w0 & 0xffff0000u); acc2 = fma(x, x, acc2);
-                    x = (double)__uint_as_float(w1 << 16); acc = fma(x, x, acc);
-                    x = (double)__uint_as_float(w1 & 0xffff0000u); acc2 = fma(x, x, acc2);
-                }
-            }
+            double x;
+            x = bf16_half_to_f64((uint16_t)(w0 & 0xffffu)); acc = fma(x, x, acc);
+            x = bf16_half_to_f64((uint16_t)(w0 >> 16)); acc2 = fma(x, x, acc2);
+            x = bf16_half_to_f64((uint16_t)(w1 & 0xffffu)); acc = fma(x, x, acc);
+            x = bf16_half_to_f64((uint16_t)(w1 >> 16)); acc2 = fma(x, x, acc2);
         }
 }
 
-template <int kVar>
+// `scale` = 2^-2k, applied to each thread's sum.
 __global__ void __launch_bounds__(kBlock)
 norm_pow2_bf16_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks, uint32_t nchunks,
-                      Pow2Scale scale, double max_norm, int finalize, NormOut out)
+                      double scale, double max_norm, int finalize, NormOut out)
 {
     double acc = 0.0, acc2 = 0.0;
-    uint32_t mx = 0;
     const uint32_t stride = gridDim.x * kNormBatch;
     for (uint32_t c0 = blockIdx.x * kNormBatch; c0 < nchunks; c0 += stride) {
         const char *base[kNormBatch];
@@ -734,9 +688,9 @@ norm_pow2_bf16_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restr
             }
             full &= nitems[j] == kChunkItems;
         }
-        if (full) norm_pow2_batch<kVar, true>(base, nitems, acc, acc2, mx);
-        else norm_pow2_batch<kVar, false>(base, nitems, acc, acc2, mx);
-        if (stray) {  // rare: head / tail elements one by one, through the convert, into the first chain
+        if (full) norm_pow2_batch<true>(base, nitems, acc, acc2);  // the common case carries no per-item predicates
+        else norm_pow2_batch<false>(base, nitems, acc, acc2);
+        if (stray) {  // rare: head / tail elements one by one into the first chain, as the generic kernel does
             for (int j = 0; j < kNormBatch && c0 + j < nchunks; ++j) {
                 const Chunk ck = chunks[c0 + j];
                 const TensorDesc d = descs[ck.tensor];
@@ -744,28 +698,15 @@ norm_pow2_bf16_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restr
                 for (int r = 0; r < 2; ++r) {
                     uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
                     for (uint64_t i = b + threadIdx.x; i < e; i += kBlock) {
-                        double x = (double)bf16_to_f32(((const uint16_t *)d.g)[i]);
-                        if (kVar == 3) {  // this variant's first chain carries the 2^208 factor
-                            x *= 0x1p104;
-                            if ((__double2hiint(x) & 0x7ff00000) == 0x7ff00000) mx = 0x7fff7fffu;
-                            else acc = fma(x, x, acc);
-                        } else {
-                            acc = fma(x, x, acc);
-                        }
+                        double x = bf16_half_to_f64(((const uint16_t *)d.g)[i]);
+                        acc = fma(x, x, acc);
                     }
                 }
             }
         }
     }
-    int bad;
-    if (kVar == 3) {
-        bad = ((mx & 0xffffu) >= 0x7f80u || (mx >> 16) >= 0x7f80u) ? 1 : 0;
-        acc = acc * scale.hi + acc2 * scale.hi;
-    } else {
-        bad = ((kVar == 2 || kVar == 5) && mx >= 0x7f800000u) ? 1 : 0;
-        acc = acc * scale.lo + acc2 * ((kVar == 2 || kVar == 5) ? scale.hi : scale.lo);
-    }
-    bad |= (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN among the converted elements
+    acc = acc * scale + acc2 * scale;
+    int bad = (__double2hiint(acc) & 0x7ff00000) == 0x7ff00000 ? 1 : 0;  // inf or NaN among the inputs
     norm_finish(acc, bad, out, max_norm, finalize);
 }
 

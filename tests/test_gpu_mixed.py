@@ -225,8 +225,8 @@ def test_large_norm_and_exact_flag(nb):
 
 @pytest.mark.parametrize("scale", [1.0, 2.0, 65536.0, 131072.0, 3.0])
 def test_power_of_two_norm_pass_has_the_generic_kernels_bits(nb, scale):
-    """With an unscale factor 2^-k, k <= 16, the synchronous step takes its norm from the kernel that builds
-    f64 values by bit placement and applies the scale to the sum; the asynchronous step (scale read from
+    """With an unscale factor 2^-k, k <= 16, the synchronous step takes its norm from the kernel that converts
+    each bf16 half straight to f64 and applies the scale to the sum; the asynchronous step (scale read from
     device memory) always runs the generic kernel that multiplies and converts every element.  Same grid,
     same accumulation order: the two norms must be the same f64, on data that holds zeros, bf16 and f32
     subnormals, the largest finite value and ordinary gradients, over several tensors with ragged ends.
