@@ -357,9 +357,46 @@ def zero1_self_check(opt, step, pflat, gflat, total, rank, world, dev, transport
                          "times f32(1/world), rounded once to bf16"}
 
 
-def peer_copy_peak(nb, opt, rank, world, dev, nbytes=1 << 30, reps=5):
-    """GB/s per GPU and direction of a plain SM copy from the next rank's gradient bucket into local memory,
-    all ranks at once (ring pattern: every GPU reads from one peer and is read by one peer)."""
+def pcie_rates(torch, dev, world, host_buf, dev_buf, barrier, max_over_ranks):
+    """Host<->device copy rates with every rank copying at the same time (GB/s per GPU, the slowest rank):
+    the floor under the end-to-end step, which has to bring every rank's whole gradient bucket in.
+    Returns (h2d alone, d2h alone, h2d while d2h runs, d2h while h2d runs)."""
+    n = min(host_buf.numel(), dev_buf.numel(), 1 << 29)
+    other = torch.empty(n, dtype=host_buf.dtype).pin_memory()
+    side = torch.cuda.Stream()
+    nbytes = n * host_buf.element_size()
+
+    def timed(fn_main, fn_side=None, reps=3):
+        best = [0.0, 0.0]
+        for _ in range(reps):
+            barrier()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            e[0].record()
+            fn_main()
+            e[1].record()
+            if fn_side is not None:
+                with torch.cuda.stream(side):
+                    e[2].record()
+                    fn_side()
+                    e[3].record()
+            torch.cuda.synchronize()
+            best[0] = max(best[0], nbytes / (e[0].elapsed_time(e[1]) * 1e-3) / 1e9)
+            if fn_side is not None:
+                best[1] = max(best[1], nbytes / (e[2].elapsed_time(e[3]) * 1e-3) / 1e9)
+        return [-max_over_ranks(-b) for b in best]                 # the slowest rank's best
+
+    h2d = lambda: dev_buf[:n].copy_(host_buf[:n], non_blocking=True)
+    d2h = lambda: other.copy_(dev_buf[n:2 * n] if dev_buf.numel() >= 2 * n else dev_buf[:n], non_blocking=True)
+    a = timed(h2d)[0]
+    b = timed(d2h)[0]
+    c = timed(h2d, d2h)
+    return a, b, c[0], c[1]
+
+
+def peer_copy_peak(nb, opt, rank, world, dev, nbytes=1 << 30, reps=5, write=False):
+    """GB/s per GPU and direction of a plain SM copy between this rank and the next rank's gradient bucket,
+    all ranks at once (ring pattern: every GPU reads from / writes to one peer and is read / written by one).
+    write=False: 128-bit loads from the peer, stores to local memory; write=True: the reverse."""
     import ctypes as C
 
     import torch
@@ -367,6 +404,10 @@ def peer_copy_peak(nb, opt, rank, world, dev, nbytes=1 << 30, reps=5):
     nbytes = min(nbytes, opt.padded * 2) // 16 * 16
     src = opt.peer_grad_ptrs[(rank + 1) % world]
     dst = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    if write:
+        src, dst_ptr = dst.data_ptr(), src
+    else:
+        dst_ptr = dst.data_ptr()
     lib = nb._lib.load()
     stream = torch.cuda.current_stream().cuda_stream
     best = 0.0
@@ -374,7 +415,7 @@ def peer_copy_peak(nb, opt, rank, world, dev, nbytes=1 << 30, reps=5):
         torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        nb._lib.check(None, lib.nbo_copy_probe(dev.index, C.c_void_p(stream), C.c_void_p(dst.data_ptr()), C.c_void_p(src),
+        nb._lib.check(None, lib.nbo_copy_probe(dev.index, C.c_void_p(stream), C.c_void_p(dst_ptr), C.c_void_p(src),
                                               nbytes))
         e1.record()
         torch.cuda.synchronize()
@@ -750,7 +791,11 @@ def run_ours(args, wl_name, wl):
                   "step_frac": 30 * total / (su + sn) / 1e6 / peak,
                   "step_frac_of_nominal_8TBs": 30 * total / (su + sn) / 1e6 / NOMINAL_HBM_GBS}
 
-    zero1_check = nvlink_peak = None
+    pcie = None
+    if wl["kind"] == "zero1" and not args.no_e2e:
+        pcie = pcie_rates(torch, dev, world, ring_in, gflat, barrier, max_over_ranks)
+
+    zero1_check = nvlink_peak = nvlink_peak_write = None
     if wl["kind"] == "zero1" and world > 1:
         if fused:
             opt.keep_reduced_grads(True)
@@ -759,6 +804,7 @@ def run_ours(args, wl_name, wl):
         zero1_check = zero1_self_check(opt, step, pflat, gflat, total, rank, world, dev, tr_name)
         if fused:
             nvlink_peak = peer_copy_peak(nb, opt, rank, world, dev)
+            nvlink_peak_write = peer_copy_peak(nb, opt, rank, world, dev, write=True)   # overwrites gradients: last use
 
     configs = None
     if wl["kind"] == "zero1" and world == 1 and rank == 0 and not args.no_configs:
@@ -804,6 +850,15 @@ def run_ours(args, wl_name, wl):
         "wall_ms_per_step": wall * 1e3 / args.steps,
     }
     line["config"].update(extra)
+    if pcie is not None:
+        # every rank must bring its whole gradient bucket in: h2d bytes per rank / the rate all ranks reach together
+        floor_s = (h2d / world) / (pcie[2] * 1e9) if pcie[2] else None
+        line["e2e"].update(h2d_gbs_all_ranks_at_once=pcie[0], d2h_gbs_all_ranks_at_once=pcie[1],
+                           h2d_gbs_while_d2h=pcie[2], d2h_gbs_while_h2d=pcie[3],
+                           h2d_gbs_achieved=(h2d / world) / e2e_s / 1e9,
+                           floor_ms=floor_s * 1e3 if floor_s else None,
+                           floor_note="per-rank gradient bytes over the host-to-device rate every rank reaches when all "
+                                      "ranks copy in both directions at once (1 GiB pinned buffers, cudaMemcpyAsync)")
     if configs is not None:
         line["configs"] = configs
     if wl["kind"] == "zero1" and world > 1:
@@ -814,6 +869,7 @@ def run_ours(args, wl_name, wl):
         per_dir = bucket * (1.0 + 1.0 / world) if tr == "mcast" else 2.0 * bucket * (world - 1) / world
         step_s = dev_s / args.steps
         line["nvlink"] = {"transport": tr, "bytes_per_gpu_per_direction": per_dir, "peak_measured": nvlink_peak,
+                          "peak_measured_stores": nvlink_peak_write,
                           "unit": "GB/s", "achieved": per_dir / step_s / 1e9,
                           "frac": per_dir / step_s / 1e9 / nvlink_peak if nvlink_peak else None,
                           "target_ms": per_dir / (nvlink_peak * 1e9) * 1e3 if nvlink_peak else None,

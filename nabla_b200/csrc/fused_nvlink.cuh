@@ -164,30 +164,9 @@ __device__ __forceinline__ bool barrier_passed(const PeerArgs &pa)
     return pa.barrier_seen == nullptr || *(const volatile int32_t *)pa.barrier_seen == pa.barrier_expect;
 }
 
-// 8-byte asynchronous copy global -> shared (LDGSTS; not the bulk / tensor-map engine).  Used to stage the
-// other ranks' gradients several chunks ahead without holding registers for them.
-__device__ __forceinline__ void cp_async_8(void *smem_dst, const void *gmem_src)
-{
-    uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
-
-// Input transports of the fused update beyond enum Transport:
-//   kPeerRing  the other ranks' gradients of the next kRingStages-1 chunks are in flight to a shared-memory
-//              ring (cp.async, 8 bytes per thread and item; every thread reads back only what it copied
-//              itself, so no CTA barrier is needed).  Remote latency is then covered by up to
-//              2 CTAs x (kRingStages-1) x 8 KiB per remote rank in flight per SM, instead of by the
-//              loads of the chunk being worked on.  For world <= kRingMaxWorld.
-enum { kPeerRing = 3 };
-#ifndef NBO_RING_STAGES
-#define NBO_RING_STAGES 4
+#ifndef NBO_MC_PREFETCH
+#define NBO_MC_PREFETCH 1  // the multicast transport issues the next chunk's multimem.ld_reduce one chunk ahead
 #endif
-constexpr int kRingStages = NBO_RING_STAGES;
-constexpr int kRingMaxWorld = 4;
-constexpr size_t ring_bytes(int world) { return (size_t)kRingStages * (size_t)(world - 1) * kChunkItems * sizeof(uint2); }
 
 struct ChunkLoc {
     TensorDesc d;
@@ -205,18 +184,18 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 
 // Fused reduce-scatter + Adam/AdamW + all-gather over this rank's shard.
 //   kIn  : where the gradient comes from - kLocal (already reduced into the local slice by an earlier
-//          pass), kPeer (plain loads issued with the chunk, any world), kPeerRing (staged ahead through
-//          shared memory) or kMcast (multimem.ld_reduce, issued one chunk ahead into registers).
+//          pass), kPeer (plain 64-bit loads from every rank, issued together with the chunk's state loads)
+//          or kMcast (multimem.ld_reduce, issued one chunk ahead into registers).
 //   kOut : how the bf16 params reach the other ranks - kPeer or kMcast.
-// All variants add the ranks' values in fp32 in rank order and round once, so kPeer and kPeerRing give
-// the same bits.
+// Staging the other ranks' gradients several chunks ahead through a shared-memory ring (cp.async, 8 bytes
+// per thread and item, 3 to 5 chunks in flight per CTA) was built and measured at world 2 on the 8 G-element
+// bucket: 33.1 ms per step against 25.5 ms for the plain loads below - asynchronous copies from peer memory
+// through shared memory move fewer bytes per second than register loads, so the ring was dropped.
 template <int kIn, int kOut>
 __global__ void __launch_bounds__(kBlock)
 zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
                           uint32_t nchunks, AdamHP hp, const StepCtrl *__restrict__ ctrl, PeerArgs pa)
 {
-    extern __shared__ __align__(16) unsigned char ring_raw[];
-    uint2 *ring = reinterpret_cast<uint2 *>(ring_raw);  // [stage][remote slot][kChunkItems]
     if (!barrier_passed(pa))
         return;
     if (pa.hp_dev != nullptr) hp = *pa.hp_dev;
@@ -227,25 +206,6 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         clip = ctrl->clip_scale;
     }
     const uint32_t mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int nremote = pa.world - 1;
-
-    // kPeerRing: start the copies of chunk number `it` of this CTA (an empty group when it does not exist)
-    auto stage_in = [&](uint32_t it) {
-        if (kIn == kPeerRing && it < mine) {
-            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
-            const char *g2 = (const char *)((const uint16_t *)l.d.g + l.cv.item0);
-            uint2 *dst = ring + (size_t)(it % kRingStages) * nremote * kChunkItems;
-            for (int q = 0; q < nremote; ++q) {
-                const char *src = g2 + pa.g_peer[q < pa.rank ? q : q + 1];
-#pragma unroll
-                for (int u = 0; u < kItemsPerThread; ++u) {
-                    uint32_t i = threadIdx.x + u * kBlock;
-                    if (i < l.cv.nitems) cp_async_8(dst + q * kChunkItems + i, src + (size_t)i * sizeof(uint2));
-                }
-            }
-        }
-        if (kIn == kPeerRing) cp_async_commit();
-    };
     uint2 gq[kIn == kMcast ? kItemsPerThread : 1];  // kMcast: the reduced gradient of the next chunk
     auto prefetch_mc = [&](uint32_t it) {
         if (kIn == kMcast && it < mine) {
@@ -258,9 +218,7 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             }
         }
     };
-    if (kIn == kPeerRing)
-        for (uint32_t it = 0; it + 1 < (uint32_t)kRingStages; ++it) stage_in(it);
-    prefetch_mc(0);
+    if (NBO_MC_PREFETCH) prefetch_mc(0);
 
     for (uint32_t it = 0; it < mine; ++it) {
         const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
@@ -278,41 +236,27 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
         if (kIn == kMcast) {
+            if (!NBO_MC_PREFETCH) prefetch_mc(it);
 #pragma unroll
             for (int u = 0; u < kItemsPerThread; ++u) g[u] = gq[kIn == kMcast ? u : 0];
-            prefetch_mc(it + 1);  // in flight while this chunk is updated and published
+            if (NBO_MC_PREFETCH) prefetch_mc(it + 1);  // in flight while this chunk is updated and published
         }
-        if (kIn == kPeerRing) stage_in(it + kRingStages - 1);
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn == kLocal || kIn == kPeerRing) g[u] = ld_stream(g2 + i);  // ring: this rank's own term
+                if (kIn == kLocal) g[u] = ld_stream(g2 + i);
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
                 v[u] = ld_stream(v4 + i);
             }
         }
-        if (kIn == kPeerRing) cp_async_wait<kRingStages - 1>();  // this chunk's group (and all older ones) has landed
-        const uint2 *slot = ring + (size_t)(it % kRingStages) * nremote * kChunkItems;
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn == kPeerRing) {
-                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-                    for (int r = 0; r < pa.world; ++r) {  // rank order, as the plain peer path
-                        const uint2 x = r == pa.rank ? g[u] : slot[(r < pa.rank ? r : r - 1) * kChunkItems + i];
-                        a0 = __fadd_rn(a0, bf16_to_f32(x.x & 0xffffu));
-                        a1 = __fadd_rn(a1, bf16_to_f32(x.x >> 16));
-                        a2 = __fadd_rn(a2, bf16_to_f32(x.y & 0xffffu));
-                        a3 = __fadd_rn(a3, bf16_to_f32(x.y >> 16));
-                    }
-                    g[u].x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
-                    g[u].y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
-                }
                 if (kIn != kLocal && pa.keep_reduced) st_stream(g2 + i, g[u]);
                 mixed_elem<true>(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
@@ -337,7 +281,6 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             }
         }
     }
-    if (kIn == kPeerRing) cp_async_wait<0>();
 }
 
 // Reduce-scatter fused with the norm / non-finite pass: the reduced gradient of

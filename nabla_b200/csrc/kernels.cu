@@ -276,51 +276,31 @@ extern "C" int32_t nbo_adamw_step(int32_t device, void *stream, void *param, con
 
 // ---- ZeRO-1 fused with its collectives (fused_nvlink.cuh) ------------------------------------
 
-#ifndef NBO_PEER_RING
-#define NBO_PEER_RING 1  // 0 = the peer transport always issues its remote loads with the chunk (no staging ring)
-#endif
-
 namespace nbo {
 
 template <int kIn, int kOut>
 static int32_t launch_fused_one(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
                                 const PeerArgs &pa)
 {
-    const void *k = (const void *)zero1_fused_update_kernel<kIn, kOut>;
-    size_t smem = kIn == kPeerRing ? ring_bytes(pa.world) : 0;
-    if (smem > 48 * 1024) {
-        static std::mutex once_lock;
-        static std::map<std::pair<const void *, int>, size_t> allowed;  // per kernel and device
-        std::lock_guard<std::mutex> guard(once_lock);
-        size_t &have = allowed[{k, h->device}];
-        if (have < smem) {
-            NBO_CUDA(h, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            have = smem;
-        }
-    }
-    // 2 resident CTAs per SM as for the local update kernel (register-limited; the ring fits twice as well)
-    int grid = grid_for(h, nc, k, 2);
-    zero1_fused_update_kernel<kIn, kOut><<<grid, kBlock, smem, h->stream>>>(
+    // 2 resident CTAs per SM as for the local update kernel (register-limited)
+    int grid = grid_for(h, nc, (const void *)zero1_fused_update_kernel<kIn, kOut>, 2);
+    zero1_fused_update_kernel<kIn, kOut><<<grid, kBlock, 0, h->stream>>>(
         h->d_descs, h->d_chunks + cb, nc, hp, with_ctrl ? h->d_ctrl : nullptr, pa);
     return launched(h);
 }
 
-// in_transport: 0 local, 1 peer (staged through the shared-memory ring when the world is small enough),
-// 2 multicast; out_transport: 1 peer stores, 2 multicast stores.
+// in_transport: 0 local, 1 peer loads, 2 multicast; out_transport: 1 peer stores, 2 multicast stores.
 int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t cb, uint32_t nc, const AdamHP &hp, bool with_ctrl,
                                   const PeerArgs &pa, int in_transport, int out_transport)
 {
     if (nc == 0) return NBO_OK;
-    const bool ring = in_transport == kPeer && pa.world <= kRingMaxWorld && NBO_PEER_RING;
     if (out_transport == kMcast) {
         if (in_transport == kLocal) return launch_fused_one<kLocal, kMcast>(h, cb, nc, hp, with_ctrl, pa);
         if (in_transport == kMcast) return launch_fused_one<kMcast, kMcast>(h, cb, nc, hp, with_ctrl, pa);
-        if (ring) return launch_fused_one<kPeerRing, kMcast>(h, cb, nc, hp, with_ctrl, pa);
         return launch_fused_one<kPeer, kMcast>(h, cb, nc, hp, with_ctrl, pa);
     }
     if (in_transport == kLocal) return launch_fused_one<kLocal, kPeer>(h, cb, nc, hp, with_ctrl, pa);
     if (in_transport == kMcast) return launch_fused_one<kMcast, kPeer>(h, cb, nc, hp, with_ctrl, pa);
-    if (ring) return launch_fused_one<kPeerRing, kPeer>(h, cb, nc, hp, with_ctrl, pa);
     return launch_fused_one<kPeer, kPeer>(h, cb, nc, hp, with_ctrl, pa);
 }
 
