@@ -32,31 +32,19 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-# NCCL writes its banner and communicator log to stdout; stdout must carry the one JSON line only.  The log
-# level is left as the caller set it: the output is sent to a per-process file (NCCL_DEBUG_FILE) and rank 0
-# replays those files on stderr when the run ends, so whoever reads the run's log still sees them.
-_NCCL_LOG_DIR = None
-if "NCCL_DEBUG_FILE" not in os.environ:
-    # the ranks of one launch share a parent (the launcher), so they agree on this directory without talking
-    _NCCL_LOG_DIR = os.path.join(tempfile.gettempdir(), f"nbo_nccl_log_{os.getppid()}")
-    os.makedirs(_NCCL_LOG_DIR, exist_ok=True)
-    os.environ["NCCL_DEBUG_FILE"] = os.path.join(_NCCL_LOG_DIR, "nccl.%h.%p.log")
+# stdout must carry the one JSON line only, but libraries write there too (NCCL prints its version banner and,
+# at higher NCCL_DEBUG levels, its communicator log).  Nothing is muted or re-levelled: file descriptor 1 is
+# pointed at stderr for the whole run, so whatever a library prints still reaches the run's log, and the JSON
+# line is written to the saved original stdout at the end.
+sys.stdout.flush()
+_REAL_STDOUT = os.fdopen(os.dup(1), "w")
+os.dup2(2, 1)
 
 
-def replay_nccl_logs():
-    """Copies what NCCL wrote to its per-process log files to stderr (rank 0, end of run)."""
-    import glob
-    if _NCCL_LOG_DIR is None:
-        return
-    for path in sorted(glob.glob(os.path.join(_NCCL_LOG_DIR, "nccl.*.log"))):
-        try:
-            with open(path, errors="replace") as f:
-                text = f.read()
-            if text.strip():
-                sys.stderr.write(text if text.endswith("\n") else text + "\n")
-            os.unlink(path)
-        except OSError:
-            pass
+def emit(line: dict) -> None:
+    _REAL_STDOUT.write(json.dumps(line) + "\n")
+    _REAL_STDOUT.flush()
+
 
 # dram__bytes_read.sum + dram__bytes_write.sum per element, from the ncu captures summarised under profiles/
 # (small cases of the same kernels: 5.535 GB / 199,757,824 elements and 3.430 GB / 124,439,808 elements).
@@ -282,7 +270,7 @@ def run_reference_arm(args, wl_name, wl):
         "e2e": {"value": value, "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -852,13 +840,14 @@ def run_ours(args, wl_name, wl):
     line["config"].update(extra)
     if pcie is not None:
         # every rank must bring its whole gradient bucket in: h2d bytes per rank / the rate all ranks reach together
-        floor_s = (h2d / world) / (pcie[2] * 1e9) if pcie[2] else None
+        floor_s = (h2d / world) / (pcie[0] * 1e9) if pcie[0] else None
         line["e2e"].update(h2d_gbs_all_ranks_at_once=pcie[0], d2h_gbs_all_ranks_at_once=pcie[1],
                            h2d_gbs_while_d2h=pcie[2], d2h_gbs_while_h2d=pcie[3],
                            h2d_gbs_achieved=(h2d / world) / e2e_s / 1e9,
                            floor_ms=floor_s * 1e3 if floor_s else None,
                            floor_note="per-rank gradient bytes over the host-to-device rate every rank reaches when all "
-                                      "ranks copy in both directions at once (1 GiB pinned buffers, cudaMemcpyAsync)")
+                                      "ranks copy in at once and nothing is copied out (1 GiB pinned buffers, "
+                                      "cudaMemcpyAsync); with copy-out running the in-rate drops to h2d_gbs_while_d2h")
     if configs is not None:
         line["configs"] = configs
     if wl["kind"] == "zero1" and world > 1:
@@ -893,12 +882,10 @@ def run_ours(args, wl_name, wl):
                                 "fused_single_pass_value": sample / fused_sec,
                                 "fused_note": "the same port as one fused pass (context; not what the reference runs)"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    if rank == 0:
-        replay_nccl_logs()
 
 
 def main():
