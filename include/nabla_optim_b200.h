@@ -416,7 +416,7 @@ NBO_API int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local,
  *   nbo_symm_free   unbinds from the multicast object, unmaps and releases.  Every rank must call it
  *                   (after its last use, e.g. after a barrier) before it exits: a process must not end
  *                   while its memory is bound to a multicast object.
- * The memory is zero-initialised device memory like any other; world <= 16.  Replaces the in-process
+ * The memory is ordinary device memory with undefined initial contents; world <= 16.  Replaces the in-process
  * channel pair of nabla-train/src/dist.rs:7-34 as the way replicas reach each other's buffers. */
 typedef struct nbo_symm nbo_symm;
 NBO_API int32_t nbo_symm_token(uint8_t token_out[16]);
