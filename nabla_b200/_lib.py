@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnabla_optim_b200.so")
+# NABLA_OPTIM_B200_LIB names another build of the library (same ABI), e.g. one kept outside the package.
+LIB_PATH = os.environ.get("NABLA_OPTIM_B200_LIB") or os.path.join(_HERE, "libnabla_optim_b200.so")
 
 NBO_OK = 0
 NBO_ERR_INVALID, NBO_ERR_CUDA, NBO_ERR_NCCL, NBO_ERR_TIMEOUT, NBO_ERR_STATE, NBO_ERR_NOMEM = 1, 2, 3, 4, 5, 6
