@@ -269,6 +269,10 @@ int32_t read_ctrl(nbo_optimizer *h)
 int32_t collect_dev_state(nbo_optimizer *h)
 {
     if (!h->dev_newer) return NBO_OK;
+    if (h->zero1) {  // collectives may be pending on the stream: wait for them with the time limit first
+        int32_t rc = zero1_bounded_wait(h, "the asynchronous sharded steps");
+        if (rc != NBO_OK) return rc;
+    }
     NBO_CUDA(h, cudaMemcpyAsync(h->h_state, h->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, h->stream));
     NBO_CUDA(h, cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, sizeof(StepCtrl), cudaMemcpyDeviceToHost, h->stream));
     NBO_CUDA(h, cudaStreamSynchronize(h->stream));
@@ -804,9 +808,7 @@ int32_t nbo_step_mixed_collect(nbo_optimizer *h, nbo_step_result *result, uint64
     if (!h->dev_newer && h->h_state->ngroups == 0)
         return fail(h, NBO_ERR_STATE, "nabla-optim-b200: no asynchronous step has been enqueued");
     DeviceGuard guard(h->device);
-    int32_t rc = h->zero1 ? zero1_bounded_wait(h, "the asynchronous sharded steps") : NBO_OK;
-    if (rc != NBO_OK) return rc;
-    rc = collect_dev_state(h);
+    int32_t rc = collect_dev_state(h);
     if (rc != NBO_OK) return rc;
     const DevState &st = *h->h_state;
     if (result) {
