@@ -187,6 +187,15 @@ __device__ __forceinline__ bool barrier_passed(const PeerArgs &pa)
 #define NBO_MC_PREFETCH 1  // the multicast transport issues the next chunk's multimem.ld_reduce one chunk ahead
 #endif
 
+// kPeer2: the peer transport at world size 2.  Only one rank is remote, so its four items of the NEXT chunk fit
+// in 8 registers and are requested one chunk ahead (remote loads are then in flight all the time instead
+// of only while a chunk's loads are outstanding); the local rank's term is an ordinary load with the chunk.
+// Same sum order as kPeer: rank 0's value first, then rank 1's.
+enum { kPeer2 = 3 };
+#ifndef NBO_PEER2_PREFETCH
+#define NBO_PEER2_PREFETCH 1
+#endif
+
 #ifndef NBO_MC_WIDE
 #define NBO_MC_WIDE 0  // 1 = 16-byte multimem operations: lane pairs share one ld_reduce / st for two adjacent items
 #endif
@@ -284,8 +293,18 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         clip = ctrl->clip_scale;
     }
     const uint32_t mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    uint2 gq[kIn == kMcast ? kItemsPerThread : 1];  // kMcast: the reduced gradient of the next chunk
+    // kMcast: the reduced gradient of the next chunk; kPeer2: the remote rank's gradient of the next chunk
+    uint2 gq[(kIn == kMcast || kIn == kPeer2) ? kItemsPerThread : 1];
     auto prefetch_mc = [&](uint32_t it) {
+        if (kIn == kPeer2 && it < mine) {
+            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
+            const char *g2 = (const char *)((const uint16_t *)l.d.g + l.cv.item0) + pa.g_peer[1 - pa.rank];
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) {
+                uint32_t i = threadIdx.x + u * kBlock;
+                if (i < l.cv.nitems) gq[kIn == kPeer2 ? u : 0] = ld_peer((const uint2 *)g2 + i);
+            }
+        }
         if (kIn == kMcast && it < mine) {
             const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
             const uint2 *g2 = (const uint2 *)((const uint16_t *)l.d.g + l.cv.item0);
@@ -297,7 +316,7 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             }
         }
     };
-    if (NBO_MC_PREFETCH) prefetch_mc(0);
+    if (NBO_MC_PREFETCH || kIn == kPeer2) prefetch_mc(0);
 
     for (uint32_t it = 0; it < mine; ++it) {
         const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
@@ -314,18 +333,24 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         uint2 g[kItemsPerThread];
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
+        uint2 rg[kIn == kPeer2 ? kItemsPerThread : 1];  // kPeer2: the remote rank's term of this chunk
         if (kIn == kMcast) {
             if (!NBO_MC_PREFETCH) prefetch_mc(it);
 #pragma unroll
             for (int u = 0; u < kItemsPerThread; ++u) g[u] = gq[kIn == kMcast ? u : 0];
             if (NBO_MC_PREFETCH) prefetch_mc(it + 1);  // in flight while this chunk is updated and published
         }
+        if (kIn == kPeer2) {
+#pragma unroll
+            for (int u = 0; u < kItemsPerThread; ++u) rg[kIn == kPeer2 ? u : 0] = gq[kIn == kPeer2 ? u : 0];
+            prefetch_mc(it + 1);
+        }
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn == kLocal) g[u] = ld_stream(g2 + i);
+                if (kIn == kLocal || kIn == kPeer2) g[u] = ld_stream(g2 + i);  // kPeer2: this rank's own term
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
                 v[u] = ld_stream(v4 + i);
@@ -337,6 +362,16 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             uint2 o = make_uint2(0u, 0u);
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
+                if (kIn == kPeer2) {
+                    const uint2 r = rg[kIn == kPeer2 ? u : 0];
+                    const uint2 x0 = pa.rank == 0 ? g[u] : r, x1 = pa.rank == 0 ? r : g[u];  // rank order
+                    const float a0 = __fadd_rn(bf16_to_f32(x0.x & 0xffffu), bf16_to_f32(x1.x & 0xffffu));
+                    const float a1 = __fadd_rn(bf16_to_f32(x0.x >> 16), bf16_to_f32(x1.x >> 16));
+                    const float a2 = __fadd_rn(bf16_to_f32(x0.y & 0xffffu), bf16_to_f32(x1.y & 0xffffu));
+                    const float a3 = __fadd_rn(bf16_to_f32(x0.y >> 16), bf16_to_f32(x1.y >> 16));
+                    g[u].x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
+                    g[u].y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
+                }
                 if (kIn != kLocal && pa.keep_reduced) st_stream(g2 + i, g[u]);
                 mixed_elem<true>(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
