@@ -47,25 +47,6 @@ __device__ __forceinline__ void mc_st_b64(void *mc_addr, uint2 v)
                  : "memory");
 }
 
-__device__ __forceinline__ uint4 mc_ld_reduce_bf16x8(const void *mc_addr)
-{
-    uint4 r;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(mc_addr)
-                 : "memory");
-    return r;
-}
-
-__device__ __forceinline__ void mc_st_b128(void *mc_addr, uint4 v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
-                 :
-                 : "l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
-                   "f"(__uint_as_float(v.w))
-                 : "memory");
-}
-
 __device__ __forceinline__ uint32_t scale_round_bf16(float sum, const PeerArgs &pa)
 {
     if (pa.average) sum = __fmul_rn(sum, pa.inv_world);
@@ -183,10 +164,6 @@ __device__ __forceinline__ bool barrier_passed(const PeerArgs &pa)
     return pa.barrier_seen == nullptr || *(const volatile int32_t *)pa.barrier_seen == pa.barrier_expect;
 }
 
-#ifndef NBO_MC_PREFETCH
-#define NBO_MC_PREFETCH 1  // the multicast transport issues the next chunk's multimem.ld_reduce one chunk ahead
-#endif
-
 // kPeer2: the peer transport at world size 2.  Only one rank is remote, so its four items of the NEXT chunk fit
 // in 8 registers and are requested one chunk ahead (remote loads are then in flight all the time instead
 // of only while a chunk's loads are outstanding); the local rank's term is an ordinary load with the chunk.
@@ -195,61 +172,6 @@ enum { kPeer2 = 3 };
 #ifndef NBO_PEER2_PREFETCH
 #define NBO_PEER2_PREFETCH 1
 #endif
-
-#ifndef NBO_MC_WIDE
-#define NBO_MC_WIDE 0  // 1 = 16-byte multimem operations: lane pairs share one ld_reduce / st for two adjacent items
-#endif
-
-// 16-byte multimem operations.  Adjacent lanes hold adjacent items (8 bytes each), so the lane whose item starts
-// on a 16-byte boundary ("leader") issues one operation for itself and the next lane ("follower") and the halves
-// travel between the two by shuffle; an item without a partner (odd chunk end, warp edge when the chunk starts
-// 8 bytes off a boundary) keeps its 8-byte operation.  Every lane of the warp must call these, active or not.
-struct McRole {
-    bool leader, follower, single;
-};
-__device__ __forceinline__ McRole mc_role(const uint2 *item0_ptr, uint32_t i, uint32_t nitems)
-{
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t par = (uint32_t)(((uintptr_t)item0_ptr >> 3) & 1u);  // 1: item 0 sits 8 bytes off a 16-byte boundary
-    const bool active = i < nitems;
-    const bool even = ((i + par) & 1u) == 0u;                           // this item starts on a 16-byte boundary
-    McRole r;
-    r.leader = active && even && lane < 31u && i + 1 < nitems;
-    r.follower = active && !even && lane > 0u;
-    r.single = active && !r.leader && !r.follower;
-    return r;
-}
-
-__device__ __forceinline__ uint2 mc_apply_average(uint2 r, const PeerArgs &pa)
-{
-    if (pa.average) {
-        r.x = scale_round_bf16(bf16_to_f32(r.x & 0xffffu), pa) | (scale_round_bf16(bf16_to_f32(r.x >> 16), pa) << 16);
-        r.y = scale_round_bf16(bf16_to_f32(r.y & 0xffffu), pa) | (scale_round_bf16(bf16_to_f32(r.y >> 16), pa) << 16);
-    }
-    return r;
-}
-
-// The reduced gradient of item i (undefined for inactive lanes).
-__device__ __forceinline__ uint2 mc_load_wide(const uint2 *g2, uint32_t i, uint32_t nitems, const PeerArgs &pa)
-{
-    const McRole role = mc_role(g2, i, nitems);
-    uint4 q = make_uint4(0u, 0u, 0u, 0u);
-    if (role.leader) q = mc_ld_reduce_bf16x8((const char *)(g2 + i) + pa.g_mc);
-    uint2 mine = make_uint2(q.x, q.y);
-    const uint32_t fx = __shfl_up_sync(0xffffffffu, q.z, 1), fy = __shfl_up_sync(0xffffffffu, q.w, 1);
-    if (role.follower) mine = make_uint2(fx, fy);
-    if (role.single) mine = mc_ld_reduce_bf16x4((const char *)(g2 + i) + pa.g_mc);
-    return mc_apply_average(mine, pa);
-}
-
-// Publishes item i's parameters `v` to every rank.
-__device__ __forceinline__ void mc_store_wide(uint2 *p2, uint32_t i, uint32_t nitems, uint2 v, const PeerArgs &pa)
-{
-    const McRole role = mc_role(p2, i, nitems);
-    const uint32_t nx = __shfl_down_sync(0xffffffffu, v.x, 1), ny = __shfl_down_sync(0xffffffffu, v.y, 1);
-    if (role.leader) mc_st_b128((char *)(p2 + i) + pa.p_mc, make_uint4(v.x, v.y, nx, ny));
-    if (role.single) mc_st_b64((char *)(p2 + i) + pa.p_mc, v);
-}
 
 struct ChunkLoc {
     TensorDesc d;
@@ -268,7 +190,7 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 // Fused reduce-scatter + Adam/AdamW + all-gather over this rank's shard.
 //   kIn  : where the gradient comes from - kLocal (already reduced into the local slice by an earlier
 //          pass), kPeer (plain 64-bit loads from every rank, issued together with the chunk's state loads)
-//          or kMcast (multimem.ld_reduce, issued one chunk ahead into registers).
+//          kPeer2 (world 2, see above) or kMcast (multimem.ld_reduce, issued with the chunk's state loads).
 //   kOut : how the bf16 params reach the other ranks - kPeer or kMcast.
 // Staging the other ranks' gradients several chunks ahead through a shared-memory ring (cp.async, 8 bytes
 // per thread and item, 3 to 5 chunks in flight per CTA) was built and measured at world 2 on the 8 G-element
@@ -278,6 +200,10 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 // slice, DMA copies pushing each finished slice to the peers) was measured as well: a copy-engine push alone
 // reaches 770 GB/s per direction against 666 for SM loads and 705 for SM stores, but SM loads and a DMA push
 // running together share 677 GB/s per direction, and the step took 30.0 ms against 25.4 ms - also dropped.
+// For the multicast transport two more variants were measured on 8 GPUs (18 GB per direction): the next
+// chunk's multimem.ld_reduce issued one chunk ahead into registers, 34.4 ms, and 16-byte multimem operations
+// shared by lane pairs (halves exchanged by shuffle), 34.4 ms, against 33.3 ms for the form below; at 2 GPUs
+// they made no difference either (50.9 / 51.7 / 49.6 ms).  Both were removed.
 template <int kIn, int kOut>
 __global__ void __launch_bounds__(kBlock)
 zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
@@ -293,9 +219,8 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         clip = ctrl->clip_scale;
     }
     const uint32_t mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    // kMcast: the reduced gradient of the next chunk; kPeer2: the remote rank's gradient of the next chunk
-    uint2 gq[(kIn == kMcast || kIn == kPeer2) ? kItemsPerThread : 1];
-    auto prefetch_mc = [&](uint32_t it) {
+    uint2 gq[kIn == kPeer2 ? kItemsPerThread : 1];  // kPeer2: the remote rank's gradient of the next chunk
+    auto prefetch_remote = [&](uint32_t it) {
         if (kIn == kPeer2 && it < mine) {
             const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
             const char *g2 = (const char *)((const uint16_t *)l.d.g + l.cv.item0) + pa.g_peer[1 - pa.rank];
@@ -305,18 +230,8 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
                 if (i < l.cv.nitems) gq[kIn == kPeer2 ? u : 0] = ld_peer((const uint2 *)g2 + i);
             }
         }
-        if (kIn == kMcast && it < mine) {
-            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
-            const uint2 *g2 = (const uint2 *)((const uint16_t *)l.d.g + l.cv.item0);
-#pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (NBO_MC_WIDE) gq[kIn == kMcast ? u : 0] = mc_load_wide(g2, i, l.cv.nitems, pa);
-                else if (i < l.cv.nitems) gq[kIn == kMcast ? u : 0] = reduce_item<kMcast>(g2 + i, pa);
-            }
-        }
     };
-    if (NBO_MC_PREFETCH || kIn == kPeer2) prefetch_mc(0);
+    prefetch_remote(0);
 
     for (uint32_t it = 0; it < mine; ++it) {
         const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
@@ -334,22 +249,17 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
         uint2 rg[kIn == kPeer2 ? kItemsPerThread : 1];  // kPeer2: the remote rank's term of this chunk
-        if (kIn == kMcast) {
-            if (!NBO_MC_PREFETCH) prefetch_mc(it);
-#pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) g[u] = gq[kIn == kMcast ? u : 0];
-            if (NBO_MC_PREFETCH) prefetch_mc(it + 1);  // in flight while this chunk is updated and published
-        }
         if (kIn == kPeer2) {
 #pragma unroll
             for (int u = 0; u < kItemsPerThread; ++u) rg[kIn == kPeer2 ? u : 0] = gq[kIn == kPeer2 ? u : 0];
-            prefetch_mc(it + 1);
+            prefetch_remote(it + 1);  // in flight while this chunk is updated and published
         }
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
+                if (kIn == kMcast) g[u] = reduce_item<kMcast>(g2 + i, pa);
                 if (kIn == kLocal || kIn == kPeer2) g[u] = ld_stream(g2 + i);  // kPeer2: this rank's own term
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
@@ -359,7 +269,6 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
-            uint2 o = make_uint2(0u, 0u);
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
                 if (kIn == kPeer2) {
@@ -377,14 +286,14 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
                 mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].y & 0xffffu), w[u].z, m[u].z, v[u].z, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].y >> 16), w[u].w, m[u].w, v[u].w, hp, clip);
+                uint2 o;
                 o.x = pack_bf16x2(w[u].x, w[u].y);
                 o.y = pack_bf16x2(w[u].z, w[u].w);
                 st_stream(w4 + i, w[u]);
                 st_stream(m4 + i, m[u]);
                 st_stream(v4 + i, v[u]);
-                if (!(NBO_MC_WIDE && kOut == kMcast)) publish_item<kOut>(p2 + i, o, pa);
+                publish_item<kOut>(p2 + i, o, pa);
             }
-            if (NBO_MC_WIDE && kOut == kMcast) mc_store_wide(p2, i, cv.nitems, o, pa);  // all lanes: shuffles inside
         }
         for (int r = 0; r < 2; ++r) {
             uint64_t b = r ? cv.s_hi0 : cv.s_lo0, e = r ? cv.s_hi1 : cv.s_lo1;
