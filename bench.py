@@ -152,6 +152,15 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark(self):
+        """The timed region starts now: only samples written from here on are reported.  (The sampler itself
+        is started earlier, before the warm-up steps, because nvidia-smi takes up to a second to deliver its
+        first sample - longer than a short timed region on an 8-GPU box.)"""
+        try:
+            self.offset = os.path.getsize(self.path)
+        except (OSError, TypeError):
+            self.offset = 0
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
@@ -163,7 +172,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         try:
-            for line in open(self.path):
+            with open(self.path) as fh:
+                fh.seek(getattr(self, "offset", 0))
+                lines = fh.read().splitlines()
+            for line in lines:
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
@@ -664,15 +676,16 @@ def run_ours(args, wl_name, wl):
         staging = "whole gradient / param buffers in pinned host memory"
 
     handle.profile(True)
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(args.warmup):
         step()
-    sampler = ClockSampler(local)
     barrier()
-    sampler.start()
     launches0 = handle.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     upd_ms = norm_ms = 0.0
     barrier()
+    sampler.mark()
     ev0.record()
     t0 = time.perf_counter()
     sync_steps = wl["kind"] != "f32"      # mixed / sharded steps end with a stream sync of their own
