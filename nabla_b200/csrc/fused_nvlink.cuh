@@ -164,15 +164,6 @@ __device__ __forceinline__ bool barrier_passed(const PeerArgs &pa)
     return pa.barrier_seen == nullptr || *(const volatile int32_t *)pa.barrier_seen == pa.barrier_expect;
 }
 
-// kPeer2: the peer transport at world size 2.  Only one rank is remote, so its four items of the NEXT chunk fit
-// in 8 registers and are requested one chunk ahead (remote loads are then in flight all the time instead
-// of only while a chunk's loads are outstanding); the local rank's term is an ordinary load with the chunk.
-// Same sum order as kPeer: rank 0's value first, then rank 1's.
-enum { kPeer2 = 3 };
-#ifndef NBO_PEER2_PREFETCH
-#define NBO_PEER2_PREFETCH 1
-#endif
-
 struct ChunkLoc {
     TensorDesc d;
     ChunkView cv;
@@ -190,7 +181,7 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 // Fused reduce-scatter + Adam/AdamW + all-gather over this rank's shard.
 //   kIn  : where the gradient comes from - kLocal (already reduced into the local slice by an earlier
 //          pass), kPeer (plain 64-bit loads from every rank, issued together with the chunk's state loads)
-//          kPeer2 (world 2, see above) or kMcast (multimem.ld_reduce, issued with the chunk's state loads).
+//          or kMcast (multimem.ld_reduce, issued with the chunk's state loads).
 //   kOut : how the bf16 params reach the other ranks - kPeer or kMcast.
 // Staging the other ranks' gradients several chunks ahead through a shared-memory ring (cp.async, 8 bytes
 // per thread and item, 3 to 5 chunks in flight per CTA) was built and measured at world 2 on the 8 G-element
@@ -203,7 +194,10 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 // For the multicast transport two more variants were measured on 8 GPUs (18 GB per direction): the next
 // chunk's multimem.ld_reduce issued one chunk ahead into registers, 34.4 ms, and 16-byte multimem operations
 // shared by lane pairs (halves exchanged by shuffle), 34.4 ms, against 33.3 ms for the form below; at 2 GPUs
-// they made no difference either (50.9 / 51.7 / 49.6 ms).  Both were removed.
+// they made no difference either (50.9 / 51.7 / 49.6 ms).  Both were removed.  The same one-chunk-ahead request
+// for the single remote rank of the peer transport at 2 GPUs: 27.3 ms against 26.0 ms in the same run - removed.
+// In short: with the loads of four items per thread outstanding the links are as busy as this access pattern
+// can make them; putting more remote requests in flight only delays the stores that share the direction.
 template <int kIn, int kOut>
 __global__ void __launch_bounds__(kBlock)
 zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__restrict__ chunks,
@@ -219,20 +213,6 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         clip = ctrl->clip_scale;
     }
     const uint32_t mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    uint2 gq[kIn == kPeer2 ? kItemsPerThread : 1];  // kPeer2: the remote rank's gradient of the next chunk
-    auto prefetch_remote = [&](uint32_t it) {
-        if (kIn == kPeer2 && it < mine) {
-            const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
-            const char *g2 = (const char *)((const uint16_t *)l.d.g + l.cv.item0) + pa.g_peer[1 - pa.rank];
-#pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) {
-                uint32_t i = threadIdx.x + u * kBlock;
-                if (i < l.cv.nitems) gq[kIn == kPeer2 ? u : 0] = ld_peer((const uint2 *)g2 + i);
-            }
-        }
-    };
-    prefetch_remote(0);
-
     for (uint32_t it = 0; it < mine; ++it) {
         const ChunkLoc l = locate_chunk(descs, chunks, blockIdx.x + it * gridDim.x);
         const TensorDesc &d = l.d;
@@ -248,19 +228,13 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
         uint2 g[kItemsPerThread];
         PeerItem pg[kIn == kPeer ? kItemsPerThread : 1];
         float4 w[kItemsPerThread], m[kItemsPerThread], v[kItemsPerThread];
-        uint2 rg[kIn == kPeer2 ? kItemsPerThread : 1];  // kPeer2: the remote rank's term of this chunk
-        if (kIn == kPeer2) {
-#pragma unroll
-            for (int u = 0; u < kItemsPerThread; ++u) rg[kIn == kPeer2 ? u : 0] = gq[kIn == kPeer2 ? u : 0];
-            prefetch_remote(it + 1);  // in flight while this chunk is updated and published
-        }
 #pragma unroll
         for (int u = 0; u < kItemsPerThread; ++u) {
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) peer_prefetch(pg[kIn == kPeer ? u : 0], g2 + i, pa);
                 if (kIn == kMcast) g[u] = reduce_item<kMcast>(g2 + i, pa);
-                if (kIn == kLocal || kIn == kPeer2) g[u] = ld_stream(g2 + i);  // kPeer2: this rank's own term
+                if (kIn == kLocal) g[u] = ld_stream(g2 + i);
                 w[u] = ld_stream(w4 + i);
                 m[u] = ld_stream(m4 + i);
                 v[u] = ld_stream(v4 + i);
@@ -271,16 +245,6 @@ zero1_fused_update_kernel(const TensorDesc *__restrict__ descs, const Chunk *__r
             uint32_t i = threadIdx.x + u * kBlock;
             if (i < cv.nitems) {
                 if (kIn == kPeer) g[u] = peer_reduce(pg[kIn == kPeer ? u : 0], g2 + i, pa);
-                if (kIn == kPeer2) {
-                    const uint2 r = rg[kIn == kPeer2 ? u : 0];
-                    const uint2 x0 = pa.rank == 0 ? g[u] : r, x1 = pa.rank == 0 ? r : g[u];  // rank order
-                    const float a0 = __fadd_rn(bf16_to_f32(x0.x & 0xffffu), bf16_to_f32(x1.x & 0xffffu));
-                    const float a1 = __fadd_rn(bf16_to_f32(x0.x >> 16), bf16_to_f32(x1.x >> 16));
-                    const float a2 = __fadd_rn(bf16_to_f32(x0.y & 0xffffu), bf16_to_f32(x1.y & 0xffffu));
-                    const float a3 = __fadd_rn(bf16_to_f32(x0.y >> 16), bf16_to_f32(x1.y >> 16));
-                    g[u].x = scale_round_bf16(a0, pa) | (scale_round_bf16(a1, pa) << 16);
-                    g[u].y = scale_round_bf16(a2, pa) | (scale_round_bf16(a3, pa) << 16);
-                }
                 if (kIn != kLocal && pa.keep_reduced) st_stream(g2 + i, g[u]);
                 mixed_elem<true>(bf16_to_f32(g[u].x & 0xffffu), w[u].x, m[u].x, v[u].x, hp, clip);
                 mixed_elem<true>(bf16_to_f32(g[u].x >> 16), w[u].y, m[u].y, v[u].y, hp, clip);

@@ -294,10 +294,6 @@ int32_t launch_zero1_fused_update(nbo_optimizer *h, uint32_t cb, uint32_t nc, co
                                   const PeerArgs &pa, int in_transport, int out_transport)
 {
     if (nc == 0) return NBO_OK;
-    if (in_transport == kPeer && pa.world == 2 && NBO_PEER2_PREFETCH) {  // one remote rank: requested a chunk ahead
-        if (out_transport == kMcast) return launch_fused_one<kPeer2, kMcast>(h, cb, nc, hp, with_ctrl, pa);
-        return launch_fused_one<kPeer2, kPeer>(h, cb, nc, hp, with_ctrl, pa);
-    }
     if (out_transport == kMcast) {
         if (in_transport == kLocal) return launch_fused_one<kLocal, kMcast>(h, cb, nc, hp, with_ctrl, pa);
         if (in_transport == kMcast) return launch_fused_one<kMcast, kMcast>(h, cb, nc, hp, with_ctrl, pa);
