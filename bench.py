@@ -539,14 +539,25 @@ def run_ours(args, wl_name, wl):
             # or the runtime cannot provide symmetric memory on some rank, every rank falls back to the
             # NCCL-around-the-update path together and the line says so.
             tr = {"auto": 0, "peer": 1, "mcast": 2}[args.zero1_path]
-            ok = 1
-            try:
-                pflat, gflat = opt.attach_symmetric(transport=tr)
-            except Exception as exc:                       # noqa: BLE001 - any failure means "not available"
-                ok = 0
-                extra["fused_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
-            agree = torch.tensor([ok], device=dev)
-            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            # the buckets come from the library's own allocator (nbo_symm_alloc); torch's symmetric-memory module is
+            # the second choice
+            for how in (["native", "torch"] if args.symm == "auto" else [args.symm]):
+                ok = 1
+                try:
+                    pflat, gflat = (opt.attach_symmetric_native(transport=tr) if how == "native"
+                                    else opt.attach_symmetric(transport=tr))
+                except Exception as exc:                   # noqa: BLE001 - any failure means "not available"
+                    ok = 0
+                    extra[f"symm_{how}_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+                agree = torch.tensor([ok], device=dev)
+                dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+                if int(agree.item()) == 1:
+                    extra["symmetric_memory"] = ("nbo_symm_alloc (CUDA virtual memory + multicast, this library)"
+                                                 if how == "native" else "torch.distributed._symmetric_memory")
+                    break
+                if ok and how == "native":
+                    opt.release_symmetric()                # another rank failed: give the buckets back, all together
+                    raise SystemExit("symmetric allocation succeeded on some ranks only")
             if int(agree.item()) == 0:
                 fused = False
                 del opt
@@ -897,6 +908,9 @@ def run_ours(args, wl_name, wl):
     if rank == 0:
         emit(line)
     if world > 1:
+        if wl["kind"] == "zero1" and getattr(opt, "_native", None):
+            del pflat, gflat                               # views of memory the library is about to unmap
+            opt.release_symmetric()                        # unbind from the multicast object before any rank exits
         dist.barrier()
         dist.destroy_process_group()
 
@@ -910,6 +924,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama8b_zero1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-copy-probe", action="store_true")
+    ap.add_argument("--symm", choices=["auto", "native", "torch"], default="auto",
+                    help="N > 1, fused path: who allocates the symmetric buckets (auto = the library, then torch)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (kernel experiments)")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table of the default line")
     ap.add_argument("--zero1-path", choices=["auto", "peer", "mcast", "nccl"], default="auto",
