@@ -295,3 +295,64 @@ def test_sgd_momentum_against_an_independent_implementation(oracle):
         topt.step()
         oracle.sgd_step(p, grads[t].copy(), vel, 0.1, 0.9, 0.01)
     assert np.max(np.abs(p - tp.detach().numpy())) < 1e-12
+
+
+def _powf_half(x32: np.ndarray) -> np.ndarray:
+    """Elementwise libm powf(x, 0.5f) (what `Tensor::powf` reaches on the reference's CPU backend,
+    nabla-core/src/cpu/mod.rs:264-272); numpy's own power() short-cuts an exponent of 0.5 to sqrt."""
+    import ctypes
+    libm = ctypes.CDLL("libm.so.6")
+    libm.powf.restype = ctypes.c_float
+    libm.powf.argtypes = [ctypes.c_float, ctypes.c_float]
+    return np.array([libm.powf(float(v), 0.5) for v in x32], dtype=np.float32)
+
+
+def test_f32_adamw_sgd_bit_for_bit_against_a_second_restatement(oracle):
+    """A second restatement of AdamW / Adam / Sgd::step, written tensor op by tensor op from
+    nabla-train/src/optim/alg.rs:120-149, 283-290, 393-413 in numpy float32 (every numpy f32 operation is one
+    IEEE rounding, as every reference tensor op is; scale is x*s and axpy is y + (a*x) with the product rounded
+    first, nabla-core/src/cpu/mod.rs:211-223).  It shares no code with the C oracle; the two must agree bit for
+    bit, parameters and moments, over 40 steps including the f64 -> f32 narrowing of the step scalars."""
+    f32 = np.float32
+    rng = np.random.default_rng(7)
+    n = 3000
+    p0 = rng.normal(0, 0.5, n).astype(f32)
+    p0[::97] = 0.0                                             # parameters that sit at zero
+    grads = (rng.normal(0, 1e-2, (40, n)) * np.exp(rng.uniform(-8, 2, (40, n)))).astype(f32)
+    grads[:, ::53] = 0.0                                       # elements that never receive a gradient
+    lr, b1, b2, eps, wd = 3e-4, 0.9, 0.999, 1e-8, 0.1
+    for decoupled in (True, False):
+        p, m, v = p0.copy(), np.zeros(n, f32), np.zeros(n, f32)
+        po, mo, vo = p0.copy(), np.zeros(n, f32), np.zeros(n, f32)
+        for t in range(1, 41):
+            g = grads[t - 1]
+            # host scalars in f64, narrowed once each (alg.rs:120-135); powi is square-and-multiply
+            bc1 = 1.0 - oracle.powi(b1, t)
+            bc2 = 1.0 - oracle.powi(b2, t)
+            ss, ibc2 = f32(lr / bc1), f32(1.0 / bc2)
+            decay = f32(1.0) - f32(wd * lr)
+            m = m * f32(b1)
+            m = m + f32(1.0 - b1) * g
+            v = v * f32(b2)
+            gs = g * g
+            v = v + f32(1.0 - b2) * gs
+            d = _powf_half(v * ibc2) + f32(eps)
+            u = (m * ss) / d
+            if decoupled:
+                p = p * decay
+            p = p + f32(-1.0) * u
+            assert p.dtype == m.dtype == v.dtype == f32
+            oracle.adam_step(po, g.copy(), mo, vo, lr, b1, b2, eps, wd, step=t, decoupled=decoupled)
+            assert np.array_equal(m.view(np.uint32), mo.view(np.uint32)), (decoupled, t, "m")
+            assert np.array_equal(v.view(np.uint32), vo.view(np.uint32)), (decoupled, t, "v")
+            assert np.array_equal(p.view(np.uint32), po.view(np.uint32)), (decoupled, t, "p")
+    # Sgd::step with weight decay and momentum (alg.rs:393-413)
+    p, vel = p0.copy(), np.zeros(n, f32)
+    po, velo = p0.copy(), np.zeros(n, f32)
+    for t in range(20):
+        g = grads[t]
+        ge = g + p * f32(0.01)
+        vel = vel * f32(0.9) + ge
+        p = p + (-f32(0.1)) * vel
+        oracle.sgd_step(po, g.copy(), velo, 0.1, 0.9, 0.01)
+        assert np.array_equal(p.view(np.uint32), po.view(np.uint32)) and np.array_equal(vel.view(np.uint32), velo.view(np.uint32))
