@@ -350,7 +350,10 @@ def zero1_self_check(opt, step, pflat, gflat, total, rank, world, dev, transport
     worst = stats.clone()
     dist.all_reduce(stats, op=dist.ReduceOp.MIN)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    rel = torch.tensor([float((err / mag.clamp_min(1e-30)).max())], dtype=torch.float64, device=dev)
+    dist.all_reduce(rel, op=dist.ReduceOp.MAX)
     return {"ok": bool(stats[0] > 0 and stats[3] > 0), "reduction_within_bound": bool(stats[0] > 0),
+            "reduced_grad_max_err_over_sum_of_magnitudes": float(rel),
             "params_identical_on_all_ranks": bool(stats[3] > 0), "reduced_grad_max_ulp": int(worst[1]),
             "reduced_grad_frac_differing": float(worst[2]), "elements_per_rank": m, "bound": bound,
             "reference": "every rank's input gradients for the slice, summed in fp32 in rank order with torch, "
@@ -580,7 +583,7 @@ def run_ours(args, wl_name, wl):
             step = lambda: opt.step_ptrs(pp, gp, average=True, use_scaler=False, max_norm=0.0)
         extra["zero1_path"] = ("fused-" + args.zero1_path) if fused else ("nccl" if world > 1 else "local")
         if fused:
-            extra["zero1_transport"] = "mcast" if (tr == 2 or (tr == 0 and world >= 4 and opt.has_multicast)) else "peer"
+            extra["zero1_transport"] = "mcast" if (tr == 2 or (tr == 0 and world >= 5 and opt.has_multicast)) else "peer"
         handle = opt._h
         b, e, _ = opt.shard_range()
         local_elems = max(0, min(e, total) - b)

@@ -392,7 +392,7 @@ NBO_API int32_t nbo_zero1_step_host(nbo_optimizer *h, void *params_flat_dev, voi
  * process (`*_peers[r]` = this process's mapping of rank r's bucket, with
  * `*_peers[rank] == *_local`), optionally with an NVSwitch multicast mapping
  * (`*_mc`, may be NULL).  transport: 0 = choose (multicast when available and
- * world >= 4, else peer), 1 = plain peer loads/stores, 2 = multimem
+ * world >= 5, else peer), 1 = plain peer loads/stores, 2 = multimem
  * ld_reduce / st through the switch.  World 2..16.  Replaces
  * nabla-train/src/dist.rs:36-43 together with the update it feeds. */
 NBO_API int32_t nbo_zero1_attach_symmetric(nbo_optimizer *h, void *grads_local,
