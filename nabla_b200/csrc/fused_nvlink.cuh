@@ -9,19 +9,22 @@
 //
 //   kPeer   plain 64-bit peer loads (one per rank, summed in fp32 in rank
 //           order, rounded once to bf16) and plain peer stores.  Per GPU and
-//           direction this moves 2 x (N-1)/N x bucket bytes.  Best for N = 2.
+//           direction this moves 2 x (N-1)/N x bucket bytes.  Measured faster up to
+//           N = 4 (plain accesses run the links at ~0.65 TB/s, multimem at ~0.52).
 //   kMcast  multimem.ld_reduce (the switch adds the N copies, fp32 accumulate)
 //           and multimem.st (the switch replicates the store).  Per GPU and
-//           direction: bucket x (1 + 1/N) bytes.  Best for N >= 4.
+//           direction: bucket x (1 + 1/N) bytes.  Fewer bytes from N = 4, faster
+//           from N = 5 (measured at 8).
 //
 // Only plain loads/stores and multimem instructions touch remote memory; no
 // tensor-map or bulk-copy engine is involved.  The kernels contain no cross-GPU waits of their own; the
 // host orders them with stream-ordered NCCL barriers (see zero1.cu), so nothing
 // here can spin.
 //
-// The reduced gradient is also written back into this rank's own slice of its
-// gradient bucket (as an in-place reduce-scatter would leave it), which is what
-// the update then uses - so the value that was applied can be read back.
+// By default the reduced gradient is also written back into this rank's own
+// slice of its gradient bucket (as an in-place reduce-scatter would leave it),
+// so the value that was applied can be read back; PeerArgs::keep_reduced = 0
+// drops that write for callers that overwrite the gradients anyway.
 #pragma once
 #include "kernels.cuh"
 
