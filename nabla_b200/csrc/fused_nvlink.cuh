@@ -199,6 +199,9 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const TensorDesc *__restrict__ 
 // shared by lane pairs (halves exchanged by shuffle), 34.4 ms, against 33.3 ms for the form below; at 2 GPUs
 // they made no difference either (50.9 / 51.7 / 49.6 ms).  Both were removed.  The same one-chunk-ahead request
 // for the single remote rank of the peer transport at 2 GPUs: 27.3 ms against 26.0 ms in the same run - removed.
+// Splitting the step into a reduce launch (into the local slice) and a <kLocal, kOut> update launch per slice
+// of the shard on two streams, so that inbound and outbound traffic overlap across kernels, was slower too:
+// 31.5 against 25.3 ms (peer, 2 GPUs) and 40.6 against 39.5 ms (multicast, 4 GPUs) at the best CTA split.
 // In short: with the loads of four items per thread outstanding the links are as busy as this access pattern
 // can make them; putting more remote requests in flight only delays the stores that share the direction.
 template <int kIn, int kOut>
