@@ -110,14 +110,17 @@ static void launch_norm_one(nbo_optimizer *h, float inv_scale, double max_norm, 
                                                                   inv_scale, max_norm, finalize, out, inv_scale_dev);
 }
 
-// k with inv_scale == 2^-k exactly and 0 <= k <= 16 (the range in which the f32 product g * 2^-k is exact for
-// every finite bf16 g, so that the scale may be applied to the sum instead of to each element); -1 otherwise.
+// k with inv_scale == 2^-k exactly and 0 <= k <= kPow2MaxK; -1 otherwise.  Up to k = 16 the f32 product
+// g * 2^-k is exact for every finite bf16 g, so the scale may be applied to the sum instead of to each
+// element without a second look; from 17 on (a loss scale that has grown past its initial 2^16) that holds
+// for all but the tiniest nonzero values, which the guarded kernel finds and takes the long way.
+constexpr int kPow2MaxK = 64;
 static int pow2_unscale_exponent(float inv_scale)
 {
     int e = 0;
     if (!(inv_scale > 0.0f) || frexpf(inv_scale, &e) != 0.5f) return -1;
     int k = 1 - e;  // inv_scale = 0.5 * 2^e = 2^(e-1)
-    return (k >= 0 && k <= 16) ? k : -1;
+    return (k >= 0 && k <= kPow2MaxK) ? k : -1;
 }
 
 int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_norm, int finalize)
@@ -126,8 +129,16 @@ int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_nor
     const int k = bf16 ? pow2_unscale_exponent(inv_scale) : -1;
     if (k >= 0) {
         int grid = norm_grid(h, true);
-        norm_pow2_bf16_kernel<<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks, ldexp(1.0, -2 * k),
-                                                            max_norm, finalize, out);
+        Pow2Guard gd{0u, inv_scale, ldexp(1.0, k)};
+        if (k <= 16) {
+            norm_pow2_bf16_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
+                                                                       ldexp(1.0, -2 * k), max_norm, finalize, out, gd);
+        } else {
+            const uint32_t c = 0x8000u - ((uint32_t)(k - 15) << 7);
+            gd.guard_c = c | (c << 16);
+            norm_pow2_bf16_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
+                                                                      ldexp(1.0, -2 * k), max_norm, finalize, out, gd);
+        }
         return launched(h);
     }
     // the flag can be read off the sum only while the unscale factor cannot overflow a finite gradient

@@ -230,7 +230,7 @@ def test_power_of_two_norm_pass_has_the_generic_kernels_bits(nb, scale):
     device memory) always runs the generic kernel that multiplies and converts every element.  Same grid,
     same accumulation order: the two norms must be the same f64, on data that holds zeros, bf16 and f32
     subnormals, the largest finite value and ordinary gradients, over several tensors with ragged ends.
-    Scales 2^17 and 3 take the generic kernel on both sides."""
+    Scale 2^17 takes the guarded form of that kernel (see the next test); scale 3 the generic kernel on both sides."""
     sizes = [(1 << 24) + 3, 4096, 5, (1 << 22) - 1, 12345]
     gen = torch.Generator(device="cuda").manual_seed(7)
     gs = []
@@ -281,6 +281,59 @@ def test_power_of_two_norm_pass_has_the_generic_kernels_bits(nb, scale):
             assert not r.applied and r.nonfinite, (t, i, v)
         gs[t][i] = keep
     assert fresh().step(ps, gs, use_scaler=True, max_norm=1.0).applied
+
+
+@pytest.mark.parametrize("k", [17, 18, 24, 40, 64])
+@pytest.mark.parametrize("tiny", ["none", "sparse", "dense"])
+def test_guarded_power_of_two_norm_pass_has_the_generic_kernels_bits(nb, k, tiny):
+    """From 2^17 on, g * 2^-k is no longer exact in f32 for the tiniest nonzero bf16 values (exponent field
+    below k - 15): the power-of-two kernel tests every word for such a value and computes the batches that
+    hold one the generic kernel's way.  Compared bit for bit with the generic kernel (asynchronous step) on
+    data with no such value (fast path only), with a handful (both paths, most threads fast) and with one in
+    every few elements (slow path nearly everywhere), values just below and at the threshold included."""
+    scale = float(2 ** k)
+    sizes = [(1 << 23) + 3, 4096, 5, (1 << 21) - 1, 12345]
+    gen = torch.Generator(device="cuda").manual_seed(11 + k)
+    thr = (k - 15) << 7                                          # smallest magnitude bits that stay exact
+    gs = []
+    for n in sizes:
+        g = (torch.randn(n, device="cuda", generator=gen) * 1e-3).to(torch.bfloat16)
+        bits = g.view(torch.int16)
+        idx = torch.arange(n, device="cuda")
+        bits[idx % 7 == 0] = 0
+        bits[idx % 11 == 0] = -32768
+        bits[idx % 29 == 0] = thr                                # exactly at the threshold: exact, fast path
+        bits[idx % 31 == 0] = -32768 + thr + 1
+        if tiny == "dense":
+            bits[idx % 13 == 0] = 0x0001
+            bits[idx % 17 == 0] = thr - 1                        # just below the threshold
+            bits[idx % 19 == 0] = -32768 + 0x007f
+            bits[idx % 23 == 0] = max(thr - 0x80, 1) + 0x55      # one exponent lower, odd mantissa
+        gs.append(g)
+    if tiny == "sparse":
+        for t, i, b in ((0, 12345, 0x0001), (0, 12346, thr - 1), (0, (1 << 23) + 2, 0x0003), (3, 77, thr - 0x33),
+                        (4, 12344, 0x007f), (2, 1, thr - 1), (1, 4095, -32768 + thr - 1)):
+            gs[t].view(torch.int16)[i] = b
+    ps = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for n in sizes]
+
+    def fresh():
+        o = nb.MixedAdamW.adamw(0.0, 0.0, [(n,) for n in sizes])
+        st = o.scaler_state(); st.scale = scale; o.load_scaler_state(st)
+        return o
+    a, b = fresh(), fresh()
+    P = nb._lib.ptr_array
+    rb = b.step(ps, gs, use_scaler=True, max_norm=1.0)
+    a.step_async(P([t.data_ptr() for t in ps]), P([t.data_ptr() for t in gs]), use_scaler=True, max_norm=1.0)
+    ra = a.collect()[0]
+    assert rb.applied and ra.applied and rb.grad_norm > 0.0
+    assert ra.grad_norm == rb.grad_norm, (ra.grad_norm.hex(), rb.grad_norm.hex())
+    for t, i in ((0, 1000), (0, 1001), (3, sizes[3] - 2)):       # non-finite values still stop the step
+        keep = gs[t][i].clone()
+        for v in (float("inf"), float("nan")):
+            gs[t][i] = v
+            r = fresh().step(ps, gs, use_scaler=True, max_norm=1.0)
+            assert not r.applied and r.nonfinite, (t, i, v)
+        gs[t][i] = keep
 
 
 @pytest.mark.parametrize("offset", [0, 1])
