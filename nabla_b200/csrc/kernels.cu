@@ -134,8 +134,7 @@ int32_t launch_norm(nbo_optimizer *h, bool bf16, float inv_scale, double max_nor
             norm_pow2_bf16_kernel<false><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
                                                                        ldexp(1.0, -2 * k), max_norm, finalize, out, gd);
         } else {
-            const uint32_t c = 0x8000u - ((uint32_t)(k - 15) << 7);
-            gd.guard_c = c | (c << 16);
+            gd.limit = ((uint32_t)(k - 15) << 7) - 1u;
             norm_pow2_bf16_kernel<true><<<grid, kBlock, 0, h->stream>>>(h->d_descs, h->d_chunks, h->nchunks,
                                                                       ldexp(1.0, -2 * k), max_norm, finalize, out, gd);
         }
