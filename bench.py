@@ -648,6 +648,8 @@ def run_ours(args, wl_name, wl):
         if mixed:
             opt = nb.MixedAdamW.adamw(wl["lr"], wl["wd"], shapes)
             opt.init_master_from_params(ps)
+            if args.loss_scale:
+                st = opt.scaler_state(); st.scale = float(args.loss_scale); opt.load_scaler_state(st)
             pa, ga = nb._lib.ptr_array([t.data_ptr() for t in ps]), nb._lib.ptr_array([t.data_ptr() for t in gs])
             step = lambda: opt.step_ptrs(pa, ga, use_scaler=wl["use_scaler"], max_norm=wl["max_norm"])
         else:
@@ -929,6 +931,9 @@ def main():
     ap.add_argument("--no-copy-probe", action="store_true")
     ap.add_argument("--symm", choices=["auto", "native", "torch"], default="auto",
                     help="N > 1, fused path: who allocates the symmetric buckets (auto = the library, then torch)")
+    ap.add_argument("--loss-scale", type=float, default=0.0,
+                    help="initial loss scale of a single-GPU mixed workload (default: the scaler's own 65536); "
+                         "from 2^17 on the norm pass runs its guarded form")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (kernel experiments)")
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration table of the default line")
     ap.add_argument("--zero1-path", choices=["auto", "peer", "mcast", "nccl"], default="auto",
